@@ -1,0 +1,110 @@
+/*
+ * welvet_cuda.h — C ABI of libwelvet_cuda.so, the sm_100a backend for Welvet's Dense MatVec.
+ *
+ * Plain pointers and sizes only; this is what a cgo package (or ctypes) binds. Each entry
+ * names the reference interface it stands in for (paths inside openfluke/welvet). The
+ * reference has no plugin registry: a backend is a set of exported functions shaped like
+ * the WebGPU resident-weight cache (webgpu/affine_cache.go) plus a dispatch case in
+ * layers/dense/dense.go:100-112.
+ *
+ * Conventions (reference README.md:154 "no fallbacks", webgpu/affine_cache.go:157-203):
+ *   - every call returns 0 on success or a negative WV_E* status; wv_last_error() gives the
+ *     message for the calling thread. Nothing falls back to the CPU.
+ *   - host buffers are copied during the call and never retained (cgo pointer rule).
+ *   - a blob is addressed by a caller-chosen 64-bit key; the reference keys its caches by
+ *     the address of the *quant.Blob (webgpu/binary_cache.go:198).
+ *   - format is a quant.Format value (quant/format.go:9-39); dtype is a core.DType value
+ *     (core/dtype.go:15-17) and only matters for FormatNone (1 = f32, 2 = f16, 3 = bf16).
+ */
+#ifndef WELVET_CUDA_H
+#define WELVET_CUDA_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  WV_OK = 0,
+  WV_ESHAPE = -1,    /* bad rows/cols/lengths (reference: "size mismatch", quant/helpers.go:94-103) */
+  WV_EFORMAT = -2,   /* unknown / unsupported format or dtype (quant.ErrUnsupported, quant/errors.go:17) */
+  WV_ENOMEM = -3,    /* device cache budget full (errAffineVRAMFull, webgpu/affine_cache.go:71) */
+  WV_ECUDA = -4,     /* CUDA runtime error */
+  WV_ETIMEOUT = -5,  /* a bounded device wait ran out */
+  WV_ENOTFOUND = -6, /* key not resident */
+  WV_EINIT = -7,     /* no usable device (webgpu InitError, webgpu/dense.go:116-125) */
+  WV_EARG = -8       /* null pointer / bad argument */
+};
+
+/* Session — replaces webgpu.Available / InitError / ensure() (webgpu/dense.go:116-125,177-192). */
+int wv_init(int device);           /* bind the library to one CUDA device; idempotent */
+int wv_available(void);            /* 1 when a device is bound and usable */
+int wv_device_count(void);
+const char* wv_last_error(void);   /* thread-local text of the last failure */
+
+/* Resident packed-weight cache — replaces WarmAffineWeight / HasAffineWeight /
+ * ClearAffineWeightCache / AffineWeightCacheBytes and their binary / f32 twins
+ * (webgpu/affine_cache.go:29-154, webgpu/binary_cache.go, webgpu/f32_cache.go).
+ * The arrays are exactly quant.Blob's Raw / Scales / Mins (quant/format.go:110-131);
+ * block_weights is Blob.BlockWeights (<= 0: inferred as InferBinaryBlockWeights /
+ * InferAffineBlockWeights do, quant/binary_g128.go:79-94, quant/affine_g64.go:95-119).
+ * Uploading an existing key is a no-op, as in uploadAffineLocked (affine_cache.go:111-116). */
+int wv_blob_upload(uint64_t key, int format, int dtype, int rows, int cols, int block_weights,
+                   const void* raw, size_t nraw, const float* scales, size_t ns,
+                   const float* mins, size_t nm);
+/* Same, from the checkpoint wire form u32 ns | u32 nm | u32 nr | scales | mins | raw
+ * (weights.EncodePackedWire / DecodePackedWire, weights/packed_wire.go:30-110; FormatNone
+ * wire is the raw element array). */
+int wv_blob_upload_wire(uint64_t key, int format, int dtype, int rows, int cols,
+                        const void* wire, size_t nwire);
+/* Row shard: keeps only rows [rows*rank/world, rows*(rank+1)/world) on this device. The
+ * reference shards contiguous row ranges over goroutines the same way
+ * (layers/dense/gemv_parallel.go:24-41). The resident blob then has rows_local rows. */
+int wv_blob_upload_shard(uint64_t key, int format, int dtype, int rows, int cols, int block_weights,
+                         const void* raw, size_t nraw, const float* scales, size_t ns,
+                         const float* mins, size_t nm, int rank, int world);
+int wv_shard_range(int rows, int rank, int world, int* row_begin, int* row_end);
+int wv_blob_has(uint64_t key);     /* 1 / 0 */
+int wv_blob_evict(uint64_t key);   /* needed when Store.Pack / Convert replace s.Packed (weights/convert.go:103-124) */
+void wv_cache_clear(void);
+uint64_t wv_cache_bytes(void);     /* device bytes held by resident blobs */
+void wv_cache_set_limit(uint64_t bytes); /* 0 = no limit; beyond it uploads return WV_ENOMEM */
+/* rows, cols as resident (local rows for a shard), packed wire bytes, device bytes, and
+ * whether the chunked kernels apply (0 = ragged shape path). Any out pointer may be NULL. */
+int wv_blob_info(uint64_t key, int* rows, int* cols, uint64_t* wire_bytes, uint64_t* dev_bytes, int* chunked);
+
+/* y[batch, out] = x[batch, in] . W^T — replaces dense.MatVecPackedBlob (layers/dense/simd.go:571-614),
+ * dense.MatVecWebGPU (layers/dense/webgpu.go:36-48) and the GEMV inside dense.Forward.
+ * Host pointers, synchronous, like the reference's device path (affine_cache.go:370-445).
+ * Checks in == cols and out == rows (dense.dims, layers/dense/dense.go:129-143). */
+int wv_matvec(uint64_t key, const float* x, float* y, int batch, int in, int out);
+/* Device pointers, asynchronous on `stream` (a cudaStream_t; NULL = default stream). For
+ * chained decode and for benchmarking with inputs resident in HBM. */
+int wv_matvec_dev(uint64_t key, const float* dx, float* dy, int batch, int in, int out, void* stream);
+
+/* Dequantise the resident blob to f32 on the device and copy rows*cols floats out —
+ * quant.Unpack (quant/unpack.go:4-34); results are bit-identical to it. */
+int wv_unpack(uint64_t key, float* out_host);
+int wv_unpack_dev(uint64_t key, float* d_out, void* stream);
+
+/* quant.Pack on the device (quant/pack.go:4-31; dense.Layer.Pack, layers/dense/dense.go:84-89):
+ * packs rows x cols f32 weights (host pointer) into caller-allocated Raw / Scales / Mins of
+ * the sizes wv_pack_sizes reports. Output bytes are identical to the reference packer's. */
+int wv_pack_sizes(int format, int dtype, int block_weights, int rows, int cols,
+                  size_t* nraw, size_t* ns, size_t* nm);
+int wv_pack(int format, int dtype, int block_weights, const float* w, int rows, int cols,
+            void* raw, float* scales, float* mins);
+/* Device-side variant: d_w is a device pointer; the packed blob stays on the device and is
+ * registered under `key` without a host round trip. */
+int wv_pack_upload_dev(uint64_t key, int format, int dtype, int block_weights, const float* d_w,
+                       int rows, int cols, void* stream);
+
+/* Experiment hook: override rows-per-warp / column split / prefetch depth / grid size of the
+ * chunked GEMV (0 = built-in choice). Not part of the reference surface. */
+void wv_set_tuning(int rows_per_warp, int col_split, int depth, int grid);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

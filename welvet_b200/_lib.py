@@ -1,0 +1,84 @@
+"""ctypes binding of libwelvet_cuda.so (the C ABI declared in include/welvet_cuda.h).
+
+There is no CPU fallback: importing this module without the built library, or calling a
+compute entry without a bound sm_100 device, raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libwelvet_cuda.so")
+
+# Every symbol include/welvet_cuda.h declares.
+SYMBOLS = [
+    "wv_init", "wv_available", "wv_device_count", "wv_last_error",
+    "wv_blob_upload", "wv_blob_upload_wire", "wv_blob_upload_shard", "wv_shard_range",
+    "wv_blob_has", "wv_blob_evict", "wv_cache_clear", "wv_cache_bytes", "wv_cache_set_limit",
+    "wv_blob_info", "wv_matvec", "wv_matvec_dev", "wv_unpack", "wv_unpack_dev",
+    "wv_pack_sizes", "wv_pack", "wv_pack_upload_dev", "wv_set_tuning",
+]
+
+WV_OK, WV_ESHAPE, WV_EFORMAT, WV_ENOMEM, WV_ECUDA, WV_ETIMEOUT, WV_ENOTFOUND, WV_EINIT, WV_EARG = (
+    0, -1, -2, -3, -4, -5, -6, -7, -8)
+_NAMES = {-1: "ESHAPE", -2: "EFORMAT", -3: "ENOMEM", -4: "ECUDA", -5: "ETIMEOUT", -6: "ENOTFOUND",
+          -7: "EINIT", -8: "EARG"}
+
+
+class WelvetError(RuntimeError):
+    """A non-zero status from the C ABI (the reference returns Go `error` values)."""
+
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"welvet_cuda {_NAMES.get(code, code)}: {msg}")
+        self.code = code
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m welvet_b200.build` "
+                "(the CUDA backend has no CPU fallback)")
+        L = C.CDLL(LIB_PATH)
+        u64, i, vp, sz = C.c_uint64, C.c_int, C.c_void_p, C.c_size_t
+        L.wv_last_error.restype = C.c_char_p
+        L.wv_cache_bytes.restype = u64
+        L.wv_cache_clear.restype = None
+        L.wv_cache_set_limit.restype = None
+        L.wv_cache_set_limit.argtypes = [u64]
+        L.wv_set_tuning.restype = None
+        L.wv_set_tuning.argtypes = [i, i, i, i]
+        L.wv_init.argtypes = [i]
+        L.wv_blob_upload.argtypes = [u64, i, i, i, i, i, vp, sz, vp, sz, vp, sz]
+        L.wv_blob_upload_wire.argtypes = [u64, i, i, i, i, vp, sz]
+        L.wv_blob_upload_shard.argtypes = [u64, i, i, i, i, i, vp, sz, vp, sz, vp, sz, i, i]
+        L.wv_shard_range.argtypes = [i, i, i, C.POINTER(i), C.POINTER(i)]
+        L.wv_blob_has.argtypes = [u64]
+        L.wv_blob_evict.argtypes = [u64]
+        L.wv_blob_info.argtypes = [u64, C.POINTER(i), C.POINTER(i), C.POINTER(u64), C.POINTER(u64), C.POINTER(i)]
+        L.wv_matvec.argtypes = [u64, vp, vp, i, i, i]
+        L.wv_matvec_dev.argtypes = [u64, vp, vp, i, i, i, vp]
+        L.wv_unpack.argtypes = [u64, vp]
+        L.wv_unpack_dev.argtypes = [u64, vp, vp]
+        L.wv_pack_sizes.argtypes = [i, i, i, i, i, C.POINTER(sz), C.POINTER(sz), C.POINTER(sz)]
+        L.wv_pack.argtypes = [i, i, i, vp, i, i, vp, vp, vp]
+        L.wv_pack_upload_dev.argtypes = [u64, i, i, i, vp, i, i, vp]
+        _lib = L
+    return _lib
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise WelvetError(rc, lib().wv_last_error().decode(errors="replace"))
+
+
+def init(device: int = -1) -> None:
+    """Bind the library to a CUDA device (default: LOCAL_RANK, else 0)."""
+    if device < 0:
+        device = int(os.environ.get("LOCAL_RANK", "0"))
+    check(lib().wv_init(device))

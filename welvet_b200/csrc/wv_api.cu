@@ -1,0 +1,496 @@
+// C ABI of libwelvet_cuda.so (see include/welvet_cuda.h): session, resident packed-weight
+// cache and the MatVec / Unpack / Pack entry points. Modelled on the reference's WebGPU
+// resident caches (webgpu/affine_cache.go): one mutex around the key -> entry map, uploads
+// idempotent per key, dispatch outside the lock, hard errors and no host fallback.
+#include "wv_common.cuh"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+// ---------------------------------------------------------------- errors
+static thread_local char t_err[512] = "";
+void wv_set_error(const char* fmt, ...) {
+  va_list ap; va_start(ap, fmt); vsnprintf(t_err, sizeof t_err, fmt, ap); va_end(ap);
+}
+extern "C" const char* wv_last_error(void) { return t_err; }
+
+#define CUDA_TRY(expr)                                                                     \
+  do {                                                                                     \
+    cudaError_t e__ = (expr);                                                              \
+    if (e__ != cudaSuccess) {                                                              \
+      wv_set_error("%s: %s (%s:%d)", #expr, cudaGetErrorString(e__), __FILE__, __LINE__);  \
+      return WV_ECUDA;                                                                     \
+    }                                                                                      \
+  } while (0)
+
+// ---------------------------------------------------------------- session
+struct Entry {
+  WvDevBlob blob;
+  void* mem = nullptr;
+  size_t dev_bytes = 0, wire_bytes = 0;
+};
+static std::mutex g_mu;                // guards the map and the byte counters
+static std::mutex g_stage_mu;          // guards the host staging buffers of wv_matvec / wv_unpack
+static std::unordered_map<uint64_t, Entry> g_cache;
+static uint64_t g_cache_bytes = 0, g_cache_limit = 0;
+static int g_device = -1;
+static cudaStream_t g_stream = nullptr;
+static float *g_hx = nullptr, *g_hy = nullptr, *g_dx = nullptr, *g_dy = nullptr;
+static size_t g_hx_n = 0, g_hy_n = 0, g_dx_n = 0, g_dy_n = 0;
+
+extern "C" int wv_device_count(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) { cudaGetLastError(); return 0; }
+  return n;
+}
+
+extern "C" int wv_init(int device) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (g_device >= 0) {
+    if (device == g_device || device < 0) return WV_OK;
+    wv_set_error("wv_init: already bound to device %d", g_device);
+    return WV_EINIT;
+  }
+  int n = wv_device_count();
+  if (n <= 0) { wv_set_error("wv_init: no CUDA device"); return WV_EINIT; }
+  if (device < 0) device = 0;
+  if (device >= n) { wv_set_error("wv_init: device %d of %d", device, n); return WV_EINIT; }
+  cudaDeviceProp prop;
+  CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10) {
+    wv_set_error("wv_init: device %d is sm_%d%d; this library carries sm_100a code only", device, prop.major, prop.minor);
+    return WV_EINIT;
+  }
+  CUDA_TRY(cudaSetDevice(device));
+  CUDA_TRY(cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking));
+  g_device = device;
+  return WV_OK;
+}
+extern "C" int wv_available(void) { return g_device >= 0 ? 1 : 0; }
+
+static int ensure_init() {
+  if (g_device < 0) { wv_set_error("welvet_cuda: wv_init has not bound a device"); return WV_EINIT; }
+  cudaSetDevice(g_device);
+  return WV_OK;
+}
+
+// ---------------------------------------------------------------- sizes
+struct Sizes { size_t nraw, ns, nm; int group; long long npad; };
+
+// Lengths the reference packers produce (quant/*.go) and the padded weight count.
+static int expected_sizes(int format, int dtype, int bw, int rows, int cols, Sizes* s) {
+  if (rows <= 0 || cols <= 0) { wv_set_error("bad shape rows=%d cols=%d", rows, cols); return WV_ESHAPE; }
+  const long long n = (long long)rows * cols;
+  const WvFmtInfo fi = wv_fmt_info(format);
+  s->nraw = s->ns = s->nm = 0; s->group = fi.pgroup; s->npad = n;
+  switch (fi.kind) {
+  case WK_NONE:
+    if (format != WV_NONE) { wv_set_error("unknown format %d", format); return WV_EFORMAT; }
+    if (dtype != WV_DT_F32 && dtype != WV_DT_F16 && dtype != WV_DT_BF16) {
+      wv_set_error("FormatNone dtype %d not supported (f32, f16, bf16 only)", dtype);
+      return WV_EFORMAT;
+    }
+    s->nraw = (size_t)n * (dtype == WV_DT_F32 ? 4 : 2); s->group = 1;
+    return WV_OK;
+  case WK_CLASSIC: { long long nb = (n + 31) / 32; s->nraw = (size_t)nb * fi.wire_block; s->npad = nb * 32; return WV_OK; }
+  case WK_KQUANT: { long long nsb = (n + 255) / 256; s->nraw = (size_t)nsb * fi.wire_block; s->npad = nsb * 256; return WV_OK; }
+  case WK_IQ: {
+    long long padn = (n + fi.pgroup - 1) / fi.pgroup * fi.pgroup;
+    s->ns = (size_t)(padn / fi.pgroup); s->nraw = (size_t)((padn * (fi.bits_lo + fi.bits_hi) + 7) / 8); s->npad = padn;
+    return WV_OK;
+  }
+  case WK_TERNARY: { long long ng = (n + 15) / 16; s->ns = (size_t)ng; s->nraw = (size_t)ng * 4; s->npad = ng * 16; return WV_OK; }
+  case WK_BINARY:
+    if (bw == 128) {
+      if (cols % 128) { wv_set_error("binary g128 needs cols %% 128 == 0 (cols=%d)", cols); return WV_ESHAPE; }
+      s->group = 128; s->ns = (size_t)rows * (cols / 128); s->nraw = (size_t)rows * (cols / 32) * 4;
+    } else {
+      long long ng = (n + 31) / 32; s->group = 32; s->ns = (size_t)ng; s->nraw = (size_t)ng * 4; s->npad = ng * 32;
+    }
+    return WV_OK;
+  case WK_AFFINE: {
+    int g = bw > 0 ? bw : 64;
+    if (cols % 8 || cols % g || g % 8) { wv_set_error("affine needs cols %% 8 == 0 and cols %% group == 0 (cols=%d group=%d)", cols, g); return WV_ESHAPE; }
+    s->group = g; s->ns = s->nm = (size_t)rows * (cols / g); s->nraw = (size_t)rows * (cols / 8) * 4;
+    return WV_OK;
+  }
+  }
+  return WV_EFORMAT;
+}
+
+extern "C" int wv_pack_sizes(int format, int dtype, int block_weights, int rows, int cols, size_t* nraw, size_t* ns, size_t* nm) {
+  Sizes s;
+  int rc = expected_sizes(format, dtype, block_weights, rows, cols, &s);
+  if (rc) return rc;
+  if (nraw) *nraw = s.nraw;
+  if (ns) *ns = s.ns;
+  if (nm) *nm = s.nm;
+  return WV_OK;
+}
+
+// BlockWeights re-inference for blobs that lost it on the wire (DecodePackedWire drops it).
+static int infer_block_weights(int format, int rows, int cols, int bw, size_t ns) {
+  if (format == WV_BINARY) {  // quant/binary_g128.go:79-94
+    if (bw == 128 || bw == 32) return bw;
+    if (cols > 0 && cols % 128 == 0 && ns == (size_t)rows * (cols / 128)) return 128;
+    return 32;
+  }
+  if (format == WV_AFFINE) {  // quant/affine_g64.go:95-119
+    if (bw > 0 && cols % bw == 0 && ns == (size_t)rows * (cols / bw)) return bw;
+    if (cols % 64 == 0 && ns == (size_t)rows * (cols / 64)) return 64;
+    if (rows > 0 && ns % rows == 0) { size_t gpr = ns / rows; if (gpr > 0 && cols % gpr == 0) return (int)(cols / gpr); }
+    return bw > 0 ? bw : 64;
+  }
+  return bw;
+}
+
+// ---------------------------------------------------------------- upload
+static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+struct Plan { size_t lo, hi, p0, p1, km, total; };
+static Plan plan_layout(const WvFmtInfo& fi, int dtype, const Sizes& s, long long nchunks) {
+  Plan p{};
+  size_t off = 0;
+  auto take = [&](size_t bytes) { size_t o = off; off = align256(off + bytes); return o; };
+  if (fi.kind == WK_NONE) { p.lo = take(s.nraw + 16); p.total = off; return p; }
+  p.lo = take((size_t)nchunks * fi.bits_lo * 4);
+  p.hi = fi.bits_hi ? take((size_t)nchunks * fi.bits_hi * 4) : 0;
+  if (fi.kind == WK_CLASSIC) { p.p0 = take((size_t)nchunks * 4); p.p1 = fi.has_min ? take((size_t)nchunks * 4) : 0; }
+  else if (fi.kind == WK_KQUANT) { p.p0 = take((size_t)((nchunks + 7) / 8) * 8); p.km = take((size_t)nchunks * (fi.has_min ? 4 : 2)); }
+  else { p.p0 = take((s.ns + 2) * 4); p.p1 = s.nm ? take((s.nm + 2) * 4) : 0; }
+  p.total = off;
+  return p;
+}
+
+static int upload_locked_free(uint64_t key, int format, int dtype, int rows, int cols, int bw,
+                              const void* raw, size_t nraw, const float* scales, size_t ns,
+                              const float* mins, size_t nm) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!raw) { wv_set_error("wv_blob_upload: null raw"); return WV_EARG; }
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (g_cache.count(key)) return WV_OK;  // idempotent per key
+  }
+  const WvFmtInfo fi = wv_fmt_info(format);
+  bw = infer_block_weights(format, rows, cols, bw, ns);
+  Sizes s;
+  rc = expected_sizes(format, dtype, bw, rows, cols, &s);
+  if (rc) return rc;
+  const bool side_arrays = fi.kind == WK_IQ || fi.kind == WK_TERNARY || fi.kind == WK_BINARY || fi.kind == WK_AFFINE;
+  if (nraw < s.nraw || (side_arrays && (ns < s.ns || nm < s.nm || (s.ns && !scales) || (s.nm && !mins)))) {
+    wv_set_error("wv_blob_upload: short buffers for format %d %dx%d: raw %zu/%zu scales %zu/%zu mins %zu/%zu",
+                 format, rows, cols, nraw, s.nraw, ns, s.ns, nm, s.nm);
+    return WV_ESHAPE;
+  }
+  const long long nchunks = fi.kind == WK_NONE ? 0 : (s.npad + 31) / 32;
+  const Plan p = plan_layout(fi, dtype, s, nchunks);
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (g_cache_limit && g_cache_bytes + p.total > g_cache_limit) {
+      wv_set_error("wv_blob_upload: device weight budget full (%llu + %zu > %llu bytes)",
+                   (unsigned long long)g_cache_bytes, p.total, (unsigned long long)g_cache_limit);
+      return WV_ENOMEM;
+    }
+  }
+  unsigned char* mem = nullptr;
+  cudaError_t ce = cudaMalloc(&mem, p.total);
+  if (ce != cudaSuccess) {
+    cudaGetLastError();
+    wv_set_error("wv_blob_upload: cudaMalloc(%zu): %s", p.total, cudaGetErrorString(ce));
+    return WV_ENOMEM;
+  }
+  Entry e;
+  e.mem = mem; e.dev_bytes = p.total; e.wire_bytes = s.nraw + 4 * s.ns + 4 * s.nm;
+  WvDevBlob& b = e.blob;
+  b.format = format; b.dtype = dtype; b.rows = rows; b.cols = cols; b.group = s.group > 0 ? s.group : 1;
+  b.n = (long long)rows * cols; b.nchunks = nchunks;
+  b.lo = reinterpret_cast<uint32_t*>(mem + p.lo);
+  b.hi = fi.bits_hi ? reinterpret_cast<uint32_t*>(mem + p.hi) : nullptr;
+  b.p0 = fi.kind != WK_NONE ? reinterpret_cast<float*>(mem + p.p0) : nullptr;
+  b.p1 = p.p1 ? reinterpret_cast<float*>(mem + p.p1) : nullptr;
+  b.km = p.km ? reinterpret_cast<uint32_t*>(mem + p.km) : nullptr;
+  if (fi.kind == WK_NONE) b.fast = (cols % 8 == 0);
+  else if (fi.kind == WK_AFFINE || fi.kind == WK_BINARY) b.fast = (cols % 32 == 0) && (s.group % 32 == 0);
+  else b.fast = (cols % 32 == 0);
+
+  auto fail = [&](int code) { cudaFree(mem); return code; };
+  if (fi.kind == WK_NONE) {
+    if (cudaMemcpyAsync(mem + p.lo, raw, s.nraw, cudaMemcpyHostToDevice, g_stream) != cudaSuccess) { wv_set_error("upload copy failed"); return fail(WV_ECUDA); }
+  } else {
+    unsigned char* tmp = nullptr;
+    if (cudaMalloc(&tmp, s.nraw + 16) != cudaSuccess) { cudaGetLastError(); wv_set_error("wv_blob_upload: staging cudaMalloc(%zu) failed", s.nraw); return fail(WV_ENOMEM); }
+    bool ok = cudaMemcpyAsync(tmp, raw, s.nraw, cudaMemcpyHostToDevice, g_stream) == cudaSuccess;
+    if (ok && side_arrays) {
+      ok = cudaMemsetAsync(mem + p.p0, 0, (s.ns + 2) * 4, g_stream) == cudaSuccess &&
+           cudaMemcpyAsync(mem + p.p0, scales, s.ns * 4, cudaMemcpyHostToDevice, g_stream) == cudaSuccess;
+      if (ok && s.nm) ok = cudaMemcpyAsync(mem + p.p1, mins, s.nm * 4, cudaMemcpyHostToDevice, g_stream) == cudaSuccess;
+    }
+    if (ok) ok = wv_launch_relayout(b, tmp, s.nraw, g_stream) == WV_OK;
+    cudaError_t se = cudaStreamSynchronize(g_stream);
+    cudaFree(tmp);
+    if (!ok || se != cudaSuccess) { wv_set_error("wv_blob_upload: device re-layout failed: %s", cudaGetErrorString(se)); return fail(WV_ECUDA); }
+  }
+  if (cudaStreamSynchronize(g_stream) != cudaSuccess) { wv_set_error("upload sync failed"); return fail(WV_ECUDA); }
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (g_cache.count(key)) { cudaFree(mem); return WV_OK; }
+  g_cache[key] = e;
+  g_cache_bytes += p.total;
+  return WV_OK;
+}
+
+extern "C" int wv_blob_upload(uint64_t key, int format, int dtype, int rows, int cols, int block_weights,
+                              const void* raw, size_t nraw, const float* scales, size_t ns,
+                              const float* mins, size_t nm) {
+  return upload_locked_free(key, format, dtype, rows, cols, block_weights, raw, nraw, scales, ns, mins, nm);
+}
+
+extern "C" int wv_blob_upload_wire(uint64_t key, int format, int dtype, int rows, int cols, const void* wire, size_t n) {
+  if (!wire) { wv_set_error("wv_blob_upload_wire: null wire"); return WV_EARG; }
+  const unsigned char* w = static_cast<const unsigned char*>(wire);
+  if (format == WV_NONE) return upload_locked_free(key, format, dtype, rows, cols, 1, w, n, nullptr, 0, nullptr, 0);
+  if (n < 12) { wv_set_error("packed wire too short (%zu bytes)", n); return WV_ESHAPE; }
+  uint32_t ns, nm, nr;
+  memcpy(&ns, w, 4); memcpy(&nm, w + 4, 4); memcpy(&nr, w + 8, 4);
+  size_t need = 12 + (size_t)ns * 4 + (size_t)nm * 4 + nr;
+  if (n < need) { wv_set_error("packed wire truncated (need %zu, have %zu)", need, n); return WV_ESHAPE; }
+  // float arrays sit at offset 12: 4-byte aligned when the wire buffer is; copy if not.
+  std::vector<float> sc(ns), mn(nm);
+  if (ns) memcpy(sc.data(), w + 12, (size_t)ns * 4);
+  if (nm) memcpy(mn.data(), w + 12 + (size_t)ns * 4, (size_t)nm * 4);
+  return upload_locked_free(key, format, dtype, rows, cols, 0, w + 12 + (size_t)ns * 4 + (size_t)nm * 4, nr,
+                            sc.data(), ns, mn.data(), nm);
+}
+
+extern "C" int wv_shard_range(int rows, int rank, int world, int* row_begin, int* row_end) {
+  if (world <= 0 || rank < 0 || rank >= world || rows < 0) { wv_set_error("wv_shard_range: rank %d of %d", rank, world); return WV_EARG; }
+  if (row_begin) *row_begin = (int)((long long)rows * rank / world);
+  if (row_end) *row_end = (int)((long long)rows * (rank + 1) / world);
+  return WV_OK;
+}
+
+extern "C" int wv_blob_upload_shard(uint64_t key, int format, int dtype, int rows, int cols, int bw,
+                                    const void* raw, size_t nraw, const float* scales, size_t ns,
+                                    const float* mins, size_t nm, int rank, int world) {
+  int r0, r1;
+  int rc = wv_shard_range(rows, rank, world, &r0, &r1);
+  if (rc) return rc;
+  if (r1 <= r0) { wv_set_error("wv_blob_upload_shard: empty shard for rank %d of %d (rows=%d)", rank, world, rows); return WV_ESHAPE; }
+  const WvFmtInfo fi = wv_fmt_info(format);
+  bw = infer_block_weights(format, rows, cols, bw, ns);
+  Sizes full;
+  rc = expected_sizes(format, dtype, bw, rows, cols, &full);
+  if (rc) return rc;
+  if (nraw < full.nraw || ns < full.ns || nm < full.nm) { wv_set_error("wv_blob_upload_shard: short buffers"); return WV_ESHAPE; }
+  const long long f0 = (long long)r0 * cols, f1 = (long long)r1 * cols;
+  const int bits = fi.bits_lo + fi.bits_hi;
+  const unsigned char* rp = static_cast<const unsigned char*>(raw);
+  long long unit = 1;
+  size_t roff = 0, soff = 0;
+  switch (fi.kind) {
+  case WK_NONE: roff = (size_t)f0 * (dtype == WV_DT_F32 ? 4 : 2); break;
+  case WK_CLASSIC: unit = 32; roff = (size_t)(f0 / 32) * fi.wire_block; break;
+  case WK_KQUANT: unit = 256; roff = (size_t)(f0 / 256) * fi.wire_block; break;
+  case WK_IQ: unit = fi.pgroup; while ((unit * bits) % 8) unit *= 2; roff = (size_t)(f0 * bits / 8); soff = (size_t)(f0 / fi.pgroup); break;
+  case WK_TERNARY: unit = 16; roff = (size_t)(f0 / 16) * 4; soff = (size_t)(f0 / 16); break;
+  case WK_BINARY: unit = full.group; roff = (size_t)(f0 / 32) * 4; soff = (size_t)(f0 / full.group); break;
+  case WK_AFFINE: unit = full.group; roff = (size_t)(f0 / 8) * 4; soff = (size_t)(f0 / full.group); break;
+  }
+  if (f0 % unit || (f1 % unit && r1 != rows)) {
+    wv_set_error("wv_blob_upload_shard: row range [%d,%d) of %dx%d splits a %lld-weight block", r0, r1, rows, cols, unit);
+    return WV_ESHAPE;
+  }
+  Sizes part;
+  rc = expected_sizes(format, dtype, bw, r1 - r0, cols, &part);
+  if (rc) return rc;
+  return upload_locked_free(key, format, dtype, r1 - r0, cols, bw, rp + roff, part.nraw,
+                            part.ns ? scales + soff : nullptr, part.ns,
+                            part.nm ? mins + soff : nullptr, part.nm);
+}
+
+extern "C" int wv_blob_has(uint64_t key) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  return g_cache.count(key) ? 1 : 0;
+}
+extern "C" int wv_blob_evict(uint64_t key) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_cache.find(key);
+  if (it == g_cache.end()) { wv_set_error("wv_blob_evict: key %llu not resident", (unsigned long long)key); return WV_ENOTFOUND; }
+  if (g_device >= 0) { cudaSetDevice(g_device); cudaDeviceSynchronize(); cudaFree(it->second.mem); }
+  g_cache_bytes -= it->second.dev_bytes;
+  g_cache.erase(it);
+  return WV_OK;
+}
+extern "C" void wv_cache_clear(void) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (g_device >= 0) { cudaSetDevice(g_device); cudaDeviceSynchronize(); }
+  for (auto& kv : g_cache) cudaFree(kv.second.mem);
+  g_cache.clear();
+  g_cache_bytes = 0;
+}
+extern "C" uint64_t wv_cache_bytes(void) { std::lock_guard<std::mutex> lk(g_mu); return g_cache_bytes; }
+extern "C" void wv_cache_set_limit(uint64_t bytes) { std::lock_guard<std::mutex> lk(g_mu); g_cache_limit = bytes; }
+
+static int lookup(uint64_t key, Entry* out) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_cache.find(key);
+  if (it == g_cache.end()) { wv_set_error("key %llu not resident", (unsigned long long)key); return WV_ENOTFOUND; }
+  *out = it->second;
+  return WV_OK;
+}
+
+extern "C" int wv_blob_info(uint64_t key, int* rows, int* cols, uint64_t* wire_bytes, uint64_t* dev_bytes, int* chunked) {
+  Entry e;
+  int rc = lookup(key, &e);
+  if (rc) return rc;
+  if (rows) *rows = e.blob.rows;
+  if (cols) *cols = e.blob.cols;
+  if (wire_bytes) *wire_bytes = e.wire_bytes;
+  if (dev_bytes) *dev_bytes = e.dev_bytes;
+  if (chunked) *chunked = e.blob.fast;
+  return WV_OK;
+}
+
+// ---------------------------------------------------------------- matvec
+static int check_dims(const Entry& e, int batch, int in, int out) {
+  if (batch <= 0 || in != e.blob.cols || out != e.blob.rows) {  // dense.dims, layers/dense/dense.go:129-143
+    wv_set_error("matvec: size mismatch rows=%d cols=%d batch=%d in=%d out=%d", e.blob.rows, e.blob.cols, batch, in, out);
+    return WV_ESHAPE;
+  }
+  return WV_OK;
+}
+
+extern "C" int wv_matvec_dev(uint64_t key, const float* dx, float* dy, int batch, int in, int out, void* stream) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!dx || !dy) { wv_set_error("wv_matvec_dev: null pointer"); return WV_EARG; }
+  Entry e;
+  if ((rc = lookup(key, &e))) return rc;
+  if ((rc = check_dims(e, batch, in, out))) return rc;
+  rc = wv_launch_gemv(e.blob, dx, dy, batch, 0, e.blob.rows, static_cast<cudaStream_t>(stream));
+  if (rc) wv_set_error("wv_matvec_dev: launch failed (%d): %s", rc, cudaGetErrorString(cudaGetLastError()));
+  return rc;
+}
+
+static int grow(float** p, size_t* cap, size_t n, bool pinned) {
+  if (*cap >= n) return WV_OK;
+  if (*p) { if (pinned) cudaFreeHost(*p); else cudaFree(*p); *p = nullptr; *cap = 0; }
+  size_t want = n + n / 2 + 1024;
+  cudaError_t e = pinned ? cudaMallocHost(p, want * 4) : cudaMalloc(p, want * 4);
+  if (e != cudaSuccess) { cudaGetLastError(); wv_set_error("staging allocation of %zu floats failed: %s", want, cudaGetErrorString(e)); return WV_ENOMEM; }
+  *cap = want;
+  return WV_OK;
+}
+
+extern "C" int wv_matvec(uint64_t key, const float* x, float* y, int batch, int in, int out) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!x || !y) { wv_set_error("wv_matvec: null pointer"); return WV_EARG; }
+  Entry e;
+  if ((rc = lookup(key, &e))) return rc;
+  if ((rc = check_dims(e, batch, in, out))) return rc;
+  const size_t nx = (size_t)batch * in, ny = (size_t)batch * out;
+  std::lock_guard<std::mutex> lk(g_stage_mu);
+  if ((rc = grow(&g_hx, &g_hx_n, nx, true)) || (rc = grow(&g_hy, &g_hy_n, ny, true)) ||
+      (rc = grow(&g_dx, &g_dx_n, nx, false)) || (rc = grow(&g_dy, &g_dy_n, ny, false))) return rc;
+  memcpy(g_hx, x, nx * 4);
+  CUDA_TRY(cudaMemcpyAsync(g_dx, g_hx, nx * 4, cudaMemcpyHostToDevice, g_stream));
+  rc = wv_launch_gemv(e.blob, g_dx, g_dy, batch, 0, e.blob.rows, g_stream);
+  if (rc) { wv_set_error("wv_matvec: launch failed (%d): %s", rc, cudaGetErrorString(cudaGetLastError())); return rc; }
+  CUDA_TRY(cudaMemcpyAsync(g_hy, g_dy, ny * 4, cudaMemcpyDeviceToHost, g_stream));
+  CUDA_TRY(cudaStreamSynchronize(g_stream));
+  memcpy(y, g_hy, ny * 4);
+  return WV_OK;
+}
+
+// ---------------------------------------------------------------- unpack
+extern "C" int wv_unpack_dev(uint64_t key, float* d_out, void* stream) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!d_out) { wv_set_error("wv_unpack_dev: null pointer"); return WV_EARG; }
+  Entry e;
+  if ((rc = lookup(key, &e))) return rc;
+  return wv_launch_unpack(e.blob, d_out, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int wv_unpack(uint64_t key, float* out_host) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!out_host) { wv_set_error("wv_unpack: null pointer"); return WV_EARG; }
+  Entry e;
+  if ((rc = lookup(key, &e))) return rc;
+  float* d = nullptr;
+  cudaError_t ce = cudaMalloc(&d, (size_t)e.blob.n * 4);
+  if (ce != cudaSuccess) { cudaGetLastError(); wv_set_error("wv_unpack: cudaMalloc(%lld floats): %s", e.blob.n, cudaGetErrorString(ce)); return WV_ENOMEM; }
+  rc = wv_launch_unpack(e.blob, d, g_stream);
+  cudaError_t c2 = cudaMemcpyAsync(out_host, d, (size_t)e.blob.n * 4, cudaMemcpyDeviceToHost, g_stream);
+  cudaError_t c3 = cudaStreamSynchronize(g_stream);
+  cudaFree(d);
+  if (rc || c2 != cudaSuccess || c3 != cudaSuccess) { wv_set_error("wv_unpack failed: %s", cudaGetErrorString(c3 != cudaSuccess ? c3 : c2)); return rc ? rc : WV_ECUDA; }
+  return WV_OK;
+}
+
+// ---------------------------------------------------------------- pack
+extern "C" int wv_pack(int format, int dtype, int bw, const float* w, int rows, int cols, void* raw, float* scales, float* mins) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!w || !raw) { wv_set_error("wv_pack: null pointer"); return WV_EARG; }
+  Sizes s;
+  if ((rc = expected_sizes(format, dtype, bw, rows, cols, &s))) return rc;
+  if ((s.ns && !scales) || (s.nm && !mins)) { wv_set_error("wv_pack: format %d needs scales/mins buffers", format); return WV_EARG; }
+  const size_t n = (size_t)rows * cols;
+  float* dw = nullptr; unsigned char* dr = nullptr; float *ds = nullptr, *dm = nullptr;
+  auto cleanup = [&]() { cudaFree(dw); cudaFree(dr); cudaFree(ds); cudaFree(dm); };
+  if (cudaMalloc(&dw, n * 4) != cudaSuccess || cudaMalloc(&dr, s.nraw + 16) != cudaSuccess ||
+      cudaMalloc(&ds, (s.ns + 1) * 4) != cudaSuccess || cudaMalloc(&dm, (s.nm + 1) * 4) != cudaSuccess) {
+    cudaGetLastError(); cleanup(); wv_set_error("wv_pack: device allocation failed"); return WV_ENOMEM;
+  }
+  bool ok = cudaMemcpyAsync(dw, w, n * 4, cudaMemcpyHostToDevice, g_stream) == cudaSuccess &&
+            cudaMemsetAsync(dr, 0, s.nraw, g_stream) == cudaSuccess;
+  if (ok) rc = wv_launch_pack(format, dtype, s.group, dw, rows, cols, dr, ds, dm, g_stream);
+  if (ok && !rc) {
+    ok = cudaMemcpyAsync(raw, dr, s.nraw, cudaMemcpyDeviceToHost, g_stream) == cudaSuccess;
+    if (ok && s.ns) ok = cudaMemcpyAsync(scales, ds, s.ns * 4, cudaMemcpyDeviceToHost, g_stream) == cudaSuccess;
+    if (ok && s.nm) ok = cudaMemcpyAsync(mins, dm, s.nm * 4, cudaMemcpyDeviceToHost, g_stream) == cudaSuccess;
+  }
+  cudaError_t se = cudaStreamSynchronize(g_stream);
+  cleanup();
+  if (rc) return rc;
+  if (!ok || se != cudaSuccess) { wv_set_error("wv_pack failed: %s", cudaGetErrorString(se)); return WV_ECUDA; }
+  return WV_OK;
+}
+
+extern "C" int wv_pack_upload_dev(uint64_t key, int format, int dtype, int bw, const float* d_w, int rows, int cols, void* stream) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!d_w) { wv_set_error("wv_pack_upload_dev: null pointer"); return WV_EARG; }
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (g_cache.count(key)) return WV_OK;
+  }
+  Sizes s;
+  if ((rc = expected_sizes(format, dtype, bw, rows, cols, &s))) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  unsigned char* dr = nullptr; float *ds = nullptr, *dm = nullptr;
+  auto cleanup = [&]() { cudaFree(dr); cudaFree(ds); cudaFree(dm); };
+  if (cudaMalloc(&dr, s.nraw + 16) != cudaSuccess || cudaMalloc(&ds, (s.ns + 1) * 4) != cudaSuccess || cudaMalloc(&dm, (s.nm + 1) * 4) != cudaSuccess) {
+    cudaGetLastError(); cleanup(); wv_set_error("wv_pack_upload_dev: device allocation failed"); return WV_ENOMEM;
+  }
+  cudaMemsetAsync(dr, 0, s.nraw, st);
+  rc = wv_launch_pack(format, dtype, s.group, d_w, rows, cols, dr, ds, dm, st);
+  if (cudaStreamSynchronize(st) != cudaSuccess) rc = rc ? rc : WV_ECUDA;
+  if (rc) { cleanup(); wv_set_error("wv_pack_upload_dev: pack failed (%d)", rc); return rc; }
+  // Reuse the normal upload path from a host bounce of the packed arrays: packed blobs are
+  // 4-25x smaller than the f32 source, and upload is a one-time cost per blob.
+  std::vector<unsigned char> hr(s.nraw);
+  std::vector<float> hs(s.ns), hm(s.nm);
+  cudaMemcpy(hr.data(), dr, s.nraw, cudaMemcpyDeviceToHost);
+  if (s.ns) cudaMemcpy(hs.data(), ds, s.ns * 4, cudaMemcpyDeviceToHost);
+  if (s.nm) cudaMemcpy(hm.data(), dm, s.nm * 4, cudaMemcpyDeviceToHost);
+  cleanup();
+  return upload_locked_free(key, format, dtype, rows, cols, s.group, hr.data(), s.nraw, hs.data(), s.ns, hm.data(), s.nm);
+}

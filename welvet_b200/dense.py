@@ -1,0 +1,113 @@
+"""Host-side mirror of the reference's layers/dense call surface, with the CUDA backend
+as an explicit dispatch case next to the reference's CPU / SIMD / WebGPU ones
+(layers/dense/dense.go:100-112). Only the forward path exists here; the GEMV runs in
+libwelvet_cuda.so and nothing falls back to the host."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional, Tuple
+
+import numpy as np
+
+from . import _lib, quant, weights
+from ._lib import WelvetError, check, lib
+
+# core.Backend (core/layer.go:125-131) plus the new value.
+BackendCPUTiled, BackendSIMD, BackendWebGPU, BackendCUDA = 0, 1, 2, 3
+# core.ActivationType values used by Dense heads (core/activate.go)
+ActivationLinear, ActivationReLU, ActivationSigmoid, ActivationTanh = 0, 1, 2, 3
+
+
+@dataclass
+class ExecConfig:  # core.ExecConfig (core/layer.go:147-153)
+    Backend: int = BackendCUDA
+    MultiCore: bool = True
+    TileSize: int = 32
+
+
+@dataclass(eq=False)
+class Layer:  # dense.Layer (layers/dense/dense.go:12-19)
+    InputHeight: int
+    OutputHeight: int
+    Activation: int
+    Weights: weights.Store
+    Exec: ExecConfig = field(default_factory=ExecConfig)
+
+
+def NewConfigured(in_: int, out: int, act: int, dt: int, format: quant.Format, init, block_weights: int = 0) -> Layer:
+    """dense.NewConfigured (layers/dense/dense.go:47-69)."""
+    ws = weights.New(out, in_, init, dt, format, block_weights)
+    return Layer(in_, out, act, ws)
+
+
+def _dims(l: Layer, x: np.ndarray) -> Tuple[int, int, int]:
+    if x.ndim < 2:
+        raise WelvetError(_lib.WV_ESHAPE, "dense: input shape need [batch,in]")
+    batch, in_, out = x.shape[0], l.InputHeight, l.OutputHeight
+    if x.shape[1] != in_:
+        raise WelvetError(_lib.WV_ESHAPE, f"dense: input width {x.shape[1]} != layer in {in_}")
+    if l.Weights.Rows != out or l.Weights.Cols != in_:
+        raise WelvetError(_lib.WV_ESHAPE, f"dense: weight shape {l.Weights.Rows}x{l.Weights.Cols} != {out}x{in_}")
+    return batch, in_, out
+
+
+def _activate(v: np.ndarray, act: int) -> np.ndarray:
+    if act == ActivationReLU:
+        return np.maximum(v, 0)
+    if act == ActivationSigmoid:
+        return 1.0 / (1.0 + np.exp(-v))
+    if act == ActivationTanh:
+        return np.tanh(v)
+    return v
+
+
+def MatVecCUDA(s: weights.Store, x: np.ndarray, y: np.ndarray, batch: int, in_: int, out: int) -> None:
+    """Twin of dense.MatVecWebGPU (layers/dense/webgpu.go:36-48): y[batch,out] = x[batch,in] W^T."""
+    if s is None or s.Packed is None:
+        raise WelvetError(_lib.WV_EARG, "dense: nil weights")
+    if x.size < batch * in_ or y.size < batch * out:
+        raise WelvetError(_lib.WV_ESHAPE, "dense: matvec shape")
+    key = quant.EnsureResident(s.Packed)
+    xs = np.ascontiguousarray(x.reshape(-1)[: batch * in_], np.float32)
+    ys = np.empty(batch * out, np.float32)
+    check(lib().wv_matvec(key, xs.ctypes.data, ys.ctypes.data, batch, in_, out))
+    y.reshape(-1)[: batch * out] = ys
+
+
+def MatVecPackedBlob(b: quant.Blob, x: np.ndarray, y: np.ndarray) -> None:
+    """dense.MatVecPackedBlob (layers/dense/simd.go:571-614) on the CUDA backend."""
+    if b is None:
+        raise WelvetError(_lib.WV_EARG, "dense: nil packed blob")
+    if x.size < b.Cols or y.size < b.Rows:
+        raise WelvetError(_lib.WV_ESHAPE, "dense: packed matvec shape")
+    quant.MatVec(b, x, y)
+
+
+def ForwardCUDA(l: Layer, input: np.ndarray) -> Tuple[np.ndarray, np.ndarray]:
+    """Shaped like dense.ForwardWebGPU (layers/dense/webgpu.go:17-33): stage x as f32, GEMV on
+    the device, then bias + activation (applyBiasAct, dense.go:145-167). Linear / no bias
+    aliases post to pre."""
+    batch, in_, out = _dims(l, input)
+    pre = np.empty((batch, out), input.dtype)
+    y = np.empty(batch * out, np.float32)
+    MatVecCUDA(l.Weights, np.asarray(input, np.float32), y, batch, in_, out)
+    pre[...] = y.reshape(batch, out)
+    bias = l.Weights.Bias
+    if l.Activation == ActivationLinear and (bias is None or len(bias) == 0):
+        return pre, pre
+    v = pre.astype(np.float64)
+    if bias is not None and len(bias):
+        v[:, : len(bias)] += np.asarray(bias, np.float64)[:out]
+        pre[...] = v
+    post = _activate(v, l.Activation).astype(input.dtype)
+    return pre, post
+
+
+def Forward(l: Optional[Layer], input: Optional[np.ndarray]) -> Tuple[np.ndarray, np.ndarray]:
+    """dense.Forward: dispatch on Exec.Backend. Unknown backends are an error here, not a
+    silent CPU route (the reference's own rule, README.md:154)."""
+    if l is None or l.Weights is None or input is None:
+        raise WelvetError(_lib.WV_EARG, "dense: nil layer/input")
+    if l.Exec.Backend == BackendCUDA:
+        return ForwardCUDA(l, input)
+    raise WelvetError(_lib.WV_EFORMAT, f"dense: backend {l.Exec.Backend} is not provided by welvet_b200 (CUDA only)")
