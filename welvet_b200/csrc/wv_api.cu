@@ -6,6 +6,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -28,6 +29,7 @@ extern "C" const char* wv_last_error(void) { return t_err; }
   } while (0)
 
 // ---------------------------------------------------------------- session
+int wv_gemv_scratch_init(size_t bytes);  // wv_gemv.cu
 struct Entry {
   WvDevBlob blob;
   void* mem = nullptr;
@@ -67,6 +69,11 @@ extern "C" int wv_init(int device) {
   }
   CUDA_TRY(cudaSetDevice(device));
   CUDA_TRY(cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking));
+  {
+    size_t mb = 32;
+    if (const char* e = getenv("WELVET_CUDA_SCRATCH_MB")) { long v = atol(e); if (v > 0) mb = (size_t)v; }
+    if (wv_gemv_scratch_init(mb << 20) != WV_OK) { wv_set_error("wv_init: cannot allocate %zu MB of activation scratch", mb); return WV_ENOMEM; }
+  }
   g_device = device;
   return WV_OK;
 }

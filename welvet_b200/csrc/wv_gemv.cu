@@ -274,6 +274,273 @@ gemv_chunked_kernel(const WvDevBlob b, const float* __restrict__ x, float* __res
   }
 }
 
+// ------------------------------------------------------------------ integer-dot kernel
+// The f32 path above spends ~6 instructions per weight (byte permute, subtract, FMA, ...) and
+// is issue-bound far below HBM speed. Every format except IQ4_NL has small integer codes, so
+// the hot loop here is integer: activations are converted once per call into block fixed
+// point (per 32 columns: X_j = rint(x_j * 2^(22-e)), 2^e > max|x| of the block, |X_j| <= 2^22,
+// split into three byte limbs X = L0 + 256 L1 + 65536 L2 packed as int8x4 words in code-group
+// order) and each group of four codes meets its four activations in one dp4a per limb:
+// 0.75 dp4a per weight with exact integer accumulation. The limb sums are recombined in f32
+// and scaled by 2^(e-22) and the block's scale.
+//   error: |x_j - X_j 2^(e-22)| <= 2^(e-23), i.e. 2^-23 of the 32-column block maximum per
+//   element (f32's own rounding is 2^-24 of the element), and no rounding inside the dot;
+//   symmetric formats subtract mid in the integer domain (accumulators start at -mid*sum(L)),
+//   so all-zero weights give exactly 0.
+__device__ __forceinline__ int dp4a_uu(unsigned a, unsigned b, int c) {
+  int d;
+  asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ int dp4a_us(unsigned a, unsigned b, int c) {
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+template <int F> struct QCfg {
+  static constexpr WvFmtInfo fi = wv_fmt_info(F);
+  static constexpr bool HALVES = fi.pgroup == 16;                 // two parameter groups per chunk
+  static constexpr bool INT_MID = fi.mid != 0 && !fi.half_mid;    // exact integer offset
+  static constexpr int NH = HALVES ? 2 : 1;
+};
+
+// Activation record, identical in the global scratch written by xquant_kernel and in the
+// shared-memory copy every GEMV CTA makes of it (uint4 units, XS = chunks_per_row | 1):
+//   [0 , 6XS)   xq    24 int8x4 words per chunk, word t = limb*8 + k at uint4 (t>>2)*XS + c
+//   [6XS, 7XS)  meta  float4 {sf, sf*SX(all 32), sf*SX(first 16), sf*SX(second 16)}
+//   [7XS, 9XS)  ini   -mid * sum(limb l over half h), int (l*2+h) at int4 ((l*2+h)>>2)*XS + c
+//                     (only read by formats with an exact integer offset)
+// One thread converts one 32-column chunk; launched once per GEMV call, so the per-CTA
+// prologue of the GEMV is a plain 16-byte-vector copy.
+template <int BL>
+__global__ void __launch_bounds__(128) xquant_kernel(const float* __restrict__ x, int cols, int imid, uint4* __restrict__ out) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");            // x may be the previous kernel's output
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int cpr = cols >> 5, XS = cpr | 1;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cpr) return;
+  const float* xp = x + (size_t)blockIdx.y * cols + (size_t)c * 32;
+  uint4* o = out + (size_t)blockIdx.y * 9 * XS;
+  float xv[32];
+  if ((reinterpret_cast<uintptr_t>(xp) & 15) == 0) {
+#pragma unroll
+    for (int q = 0; q < 8; q++) { const float4 v = __ldg(reinterpret_cast<const float4*>(xp) + q); xv[4 * q] = v.x; xv[4 * q + 1] = v.y; xv[4 * q + 2] = v.z; xv[4 * q + 3] = v.w; }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; j++) xv[j] = __ldg(xp + j);
+  }
+  float amax = 0.f;
+  bool bad = false;
+#pragma unroll
+  for (int j = 0; j < 32; j++) { amax = fmaxf(amax, fabsf(xv[j])); bad |= !(fabsf(xv[j]) <= 3.4028234e38f); }
+  const unsigned eb = (__float_as_uint(amax) >> 23) & 0xffu;
+  float sf = 0.f, inv = 0.f;
+  if (bad) sf = __uint_as_float(0x7fc00000u);  // inf / NaN in x: the row results become NaN
+  else if (eb >= 22u) { sf = __uint_as_float((eb - 21u) << 23); inv = __uint_as_float((275u - eb) << 23); }
+  unsigned wd[24];
+#pragma unroll
+  for (int t = 0; t < 24; t++) wd[t] = 0u;
+  int sx[2] = {0, 0}, sl[3][2] = {{0, 0}, {0, 0}, {0, 0}};
+#pragma unroll
+  for (int j = 0; j < 32; j++) {
+    const int k = WvLane<BL>::k_of(j), m = WvLane<BL>::m_of(j), h = j >> 4;
+    const int X = __float2int_rn(xv[j] * inv);
+    const int L0 = X & 0xff, L1 = (X >> 8) & 0xff, L2 = X >> 16;
+    wd[k] |= (unsigned)L0 << (8 * m);
+    wd[8 + k] |= (unsigned)L1 << (8 * m);
+    wd[16 + k] |= (unsigned)(L2 & 0xff) << (8 * m);
+    sx[h] += X; sl[0][h] += L0; sl[1][h] += L1; sl[2][h] += L2;
+  }
+#pragma unroll
+  for (int q = 0; q < 6; q++) o[q * XS + c] = make_uint4(wd[4 * q], wd[4 * q + 1], wd[4 * q + 2], wd[4 * q + 3]);
+  const float4 mt = make_float4(sf, sf * (float)(sx[0] + sx[1]), sf * (float)sx[0], sf * (float)sx[1]);
+  o[6 * XS + c] = make_uint4(__float_as_uint(mt.x), __float_as_uint(mt.y), __float_as_uint(mt.z), __float_as_uint(mt.w));
+  o[7 * XS + c] = make_uint4((unsigned)(-imid * sl[0][0]), (unsigned)(-imid * sl[0][1]), (unsigned)(-imid * sl[1][0]), (unsigned)(-imid * sl[1][1]));
+  o[8 * XS + c] = make_uint4((unsigned)(-imid * sl[2][0]), (unsigned)(-imid * sl[2][1]), 0u, 0u);
+}
+
+// Work split: CTA b owns rows [n*b/grid, n*(b+1)/grid); inside the CTA, team t (S warps that
+// split the columns) owns an equal contiguous share of those rows and walks it R rows at a time.
+template <int F, int R, int S, int D>
+__global__ void __launch_bounds__(WV_GEMV_THREADS, 1)
+gemv_idot_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, float* __restrict__ y, int row_begin, int row_end) {
+  constexpr WvFmtInfo fi = wv_fmt_info(F);
+  constexpr int BL = fi.bits_lo, BH = fi.bits_hi, SPW = 8 / BL;
+  constexpr unsigned MASK = 0x01010101u * ((1u << BL) - 1u);
+  constexpr unsigned MASKH = BH ? (0x01010101u * ((1u << BH) - 1u)) << BL : 0u;
+  constexpr int NW = WV_GEMV_THREADS / 32, T = NW / S;
+  constexpr bool HALVES = QCfg<F>::HALVES, INT_MID = QCfg<F>::INT_MID;
+  constexpr int NH = QCfg<F>::NH;
+  constexpr int NREC = INT_MID ? 9 : 7;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int cpr = b.cols >> 5;
+  const int XS = cpr | 1;
+  uint4* xq = reinterpret_cast<uint4*>(smem_raw);                     // [6][XS]
+  const float4* meta = reinterpret_cast<const float4*>(xq + 6 * XS);  // [XS]
+  const int4* ini = reinterpret_cast<const int4*>(xq + 7 * XS);       // [2][XS]
+  float* team = reinterpret_cast<float*>(xq + NREC * XS);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tm = warp / S, sid = warp % S;
+  const int nrows = row_end - row_begin;
+  const int c_lo = (int)(((long long)blockIdx.x * nrows) / gridDim.x), c_hi = (int)(((long long)(blockIdx.x + 1) * nrows) / gridDim.x);
+  const int r_lo = c_lo + (int)(((long long)tm * (c_hi - c_lo)) / T), r_hi = c_lo + (int)(((long long)(tm + 1) * (c_hi - c_lo)) / T);
+  const int iters = (cpr + 32 * S - 1) / (32 * S);
+  const int nsteps = ((r_hi - r_lo + R - 1) / R) * iters;
+  float* yb = y + (size_t)blockIdx.y * b.rows + row_begin;
+  const long long cbase = (long long)row_begin * cpr;
+
+  // weights do not depend on the preceding kernel: start streaming them before waiting for x
+  FragT<F> buf[D][R];
+  int prow = r_lo, pit = 0, pleft = nsteps;
+  auto issue = [&](FragT<F> (&dst)[R]) {
+    if (pleft > 0) {
+      const int c = (pit * S + sid) * 32 + lane;
+      if (c < cpr) {
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+          const int row = min(prow + r, r_hi - 1);
+          load_frag<F>(dst[r], b, cbase + (long long)row * cpr + c);
+        }
+      }
+      --pleft;
+      if (++pit == iters) { pit = 0; prow += R; }
+    }
+  };
+#pragma unroll
+  for (int d = 0; d < D; d++) issue(buf[d]);
+
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  {
+    const uint4* src = xqg + (size_t)blockIdx.y * 9 * XS;
+    for (int i = tid; i < NREC * XS; i += WV_GEMV_THREADS) xq[i] = src[i];
+  }
+  __syncthreads();
+
+  float acc[R];
+#pragma unroll
+  for (int r = 0; r < R; r++) acc[r] = 0.f;
+  int crow = r_lo, cit = 0, parity = 0;
+  for (int s = 0; s < nsteps; s += D) {
+#pragma unroll
+    for (int d = 0; d < D; d++) {
+      if (s + d < nsteps) {
+        FragT<F> cur[R];
+#pragma unroll
+        for (int r = 0; r < R; r++) cur[r] = buf[d][r];
+        issue(buf[d]);
+        const int c = (cit * S + sid) * 32 + lane;
+        if (c < cpr) {
+          unsigned xw[24];
+#pragma unroll
+          for (int q = 0; q < 6; q++) {
+            const uint4 v = xq[q * XS + c];
+            xw[4 * q] = v.x; xw[4 * q + 1] = v.y; xw[4 * q + 2] = v.z; xw[4 * q + 3] = v.w;
+          }
+          const float4 mt = meta[c];
+          int iv[6] = {0, 0, 0, 0, 0, 0};
+          if constexpr (INT_MID) {
+            const int4 a = ini[c], bq = ini[XS + c];
+            iv[0] = a.x; iv[1] = a.y; iv[2] = a.z; iv[3] = a.w; iv[4] = bq.x; iv[5] = bq.y;
+            if constexpr (!HALVES) { iv[0] += iv[1]; iv[2] += iv[3]; iv[4] += iv[5]; }
+          }
+#pragma unroll
+          for (int r = 0; r < R; r++) {
+            const FragT<F>& f = cur[r];
+            int I[3][2];
+#pragma unroll
+            for (int l = 0; l < 3; l++) { I[l][0] = iv[l * 2]; I[l][1] = HALVES ? iv[l * 2 + 1] : 0; }
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+              const int w = k / SPW, sh = k % SPW;
+              unsigned bytes = (f.lo[w] >> (BL * sh)) & MASK;
+              if constexpr (BH > 0) {
+                const int hw = (k * BH) >> 3, hs = (k * BH) & 7;
+                unsigned hv = f.hi[hw];
+                hv = hs >= BL ? (hv >> (hs - BL)) : (hv << (BL - hs));
+                bytes |= hv & MASKH;
+              }
+              const int h = (HALVES && k >= 4) ? 1 : 0;  // first / second 16 weights of the chunk
+              I[0][h] = dp4a_uu(bytes, xw[k], I[0][h]);
+              I[1][h] = dp4a_uu(bytes, xw[8 + k], I[1][h]);
+              I[2][h] = dp4a_us(bytes, xw[16 + k], I[2][h]);
+            }
+            float val[2];
+#pragma unroll
+            for (int h = 0; h < NH; h++)
+              val[h] = fmaf(65536.0f, (float)I[2][h], (float)(I[0][h] + (I[1][h] << 8)));
+            float v;
+            if constexpr (fi.kind == WK_KQUANT) {
+              // scale bytes were remapped 0 -> 1 at upload (kquant.go:180-182: a zero group
+              // scale decodes as d/255), so no test is needed here
+              const float t = u8f(f.pr[2], 0) * val[0] + u8f(f.pr[2], 1) * val[1];
+              v = (__uint_as_float(f.pr[0]) * (1.0f / 255.0f)) * t;
+              if constexpr (fi.has_min) {
+                const unsigned mb = f.pr[2] ^ 0x80800000u;  // int8 -> biased uint8
+                const float mm = (__uint_as_float(__byte_perm(mb, 0x4B000000u, 0x7652)) - 8388736.0f) * mt.z +
+                                 (__uint_as_float(__byte_perm(mb, 0x4B000000u, 0x7653)) - 8388736.0f) * mt.w;
+                acc[r] = fmaf(__uint_as_float(f.pr[1]) * (1.0f / 127.0f), mm, acc[r]);
+              }
+              acc[r] = fmaf(mt.x, v, acc[r]);
+            } else {
+              if constexpr (fi.kind == WK_CLASSIC || fi.kind == WK_AFFINE) {
+                v = __uint_as_float(f.pr[0]) * val[0];
+                if constexpr (fi.has_min) acc[r] = fmaf(__uint_as_float(f.pr[1]), mt.y, acc[r]);
+              } else if constexpr (fi.kind == WK_TERNARY) {
+                v = __uint_as_float(f.pr[0]) * val[0] + __uint_as_float(f.pr[1]) * val[1];
+              } else if constexpr (fi.sign) {
+                v = __uint_as_float(f.pr[0]) * (2.0f * val[0]);
+                acc[r] = fmaf(-__uint_as_float(f.pr[0]), mt.y, acc[r]);
+              } else {  // IQ linear grids: (code - mid - 0.5)
+                constexpr float hm = (float)fi.mid + 0.5f;
+                if constexpr (HALVES) {
+                  v = __uint_as_float(f.pr[0]) * val[0] + __uint_as_float(f.pr[1]) * val[1];
+                  acc[r] -= hm * (__uint_as_float(f.pr[0]) * mt.z + __uint_as_float(f.pr[1]) * mt.w);
+                } else {
+                  v = __uint_as_float(f.pr[0]) * val[0];
+                  acc[r] = fmaf(-hm * __uint_as_float(f.pr[0]), mt.y, acc[r]);
+                }
+              }
+              acc[r] = fmaf(mt.x, v, acc[r]);
+            }
+          }
+        }
+        if (++cit == iters) {
+#pragma unroll
+          for (int r = 0; r < R; r++) {
+#pragma unroll
+            for (int o = 16; o; o >>= 1) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], o);
+          }
+          if constexpr (S > 1) {
+            float* slot = team + ((parity * T + tm) * S) * R;
+            if (sid > 0 && lane == 0) {
+#pragma unroll
+              for (int r = 0; r < R; r++) slot[sid * R + r] = acc[r];
+            }
+            asm volatile("bar.sync %0, %1;" ::"r"(tm + 1), "r"(32 * S) : "memory");
+            if (sid == 0) {
+#pragma unroll
+              for (int q = 1; q < S; q++) {
+#pragma unroll
+                for (int r = 0; r < R; r++) acc[r] += slot[q * R + r];
+              }
+            }
+            parity ^= 1;
+          }
+          if (sid == 0 && lane == 0) {
+#pragma unroll
+            for (int r = 0; r < R; r++) if (crow + r < r_hi) yb[crow + r] = acc[r];
+          }
+#pragma unroll
+          for (int r = 0; r < R; r++) acc[r] = 0.f;
+          cit = 0; crow += R;
+        }
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------ FormatNone f32 / f16 / bf16
 // Plain streaming GEMV: warp per R rows, lanes read consecutive 16-byte pieces.
 template <int DT, int R>
@@ -367,39 +634,92 @@ static int sm_count() {
 static int g_tune_r = 0, g_tune_s = 0, g_tune_d = 0, g_tune_grid = 0;
 extern "C" void wv_set_tuning(int r, int s, int d, int grid) { g_tune_r = r; g_tune_s = s; g_tune_d = d; g_tune_grid = grid; }
 
+// Scratch arena for quantised activations: a ring of slots, one per GEMV call. A slot is
+// reused only after the ring wraps, i.e. after (arena / slot) further calls.
+static uint4* g_xq_arena = nullptr;
+static size_t g_xq_bytes = 0, g_xq_head = 0;
+int wv_gemv_scratch_init(size_t bytes) {
+  if (g_xq_arena) return WV_OK;
+  if (cudaMalloc(&g_xq_arena, bytes) != cudaSuccess) { cudaGetLastError(); return WV_ENOMEM; }
+  g_xq_bytes = bytes; g_xq_head = 0;
+  return WV_OK;
+}
+static uint4* scratch_take(size_t bytes) {
+  bytes = (bytes + 255) & ~(size_t)255;
+  if (!g_xq_arena || bytes > g_xq_bytes) return nullptr;
+  if (g_xq_head + bytes > g_xq_bytes) g_xq_head = 0;
+  uint4* p = reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(g_xq_arena) + g_xq_head);
+  g_xq_head += bytes;
+  return p;
+}
+
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
+template <int BL>
+static int launch_xquant(const float* dx, int cols, int batch, int imid, uint4* out, cudaStream_t st) {
+  const int cpr = cols >> 5;
+  cudaError_t e = launch_pdl(xquant_kernel<BL>, dim3((cpr + 127) / 128, batch), dim3(128), 0, st, dx, cols, imid, out);
+  return e == cudaSuccess ? WV_OK : WV_ECUDA;
+}
+
 template <int F, int R, int S, int D>
 static int launch_chunked(const WvDevBlob& b, const float* dx, float* dy, int batch, int rb, int re, cudaStream_t st) {
   constexpr WvFmtInfo fi = wv_fmt_info(F);
   const int cpr = b.cols >> 5, XS = cpr | 1;
   constexpr int NW = WV_GEMV_THREADS / 32, T = NW / S;
-  size_t smem = (size_t)8 * XS * 16 + (size_t)cpr * 8 + (fi.table ? 2048 : 0) + (size_t)2 * T * S * R * 4 + 16;
-  if (smem > 227 * 1024) return WV_ESHAPE;
-  static bool attr_set = false;
-  auto kern = gemv_chunked_kernel<F, R, S, D>;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return WV_ECUDA;
-    attr_set = true;
-  }
+  int dev = 0; cudaGetDevice(&dev);
   int grid = g_tune_grid > 0 ? g_tune_grid : sm_count();
-  const int G = (re - rb + R - 1) / R;
+  const int G = fi.table ? (re - rb + R - 1) / R : (re - rb);
   if (grid > G) grid = G;
   if (grid < 1) grid = 1;
-  kern<<<dim3(grid, batch), WV_GEMV_THREADS, smem, st>>>(b, dx, dy, rb, re);
-  return cudaGetLastError() == cudaSuccess ? WV_OK : WV_ECUDA;
+  static unsigned attr_mask = 0;
+  if constexpr (fi.table) {
+    const size_t smem = (size_t)8 * XS * 16 + (size_t)cpr * 8 + 2048 + (size_t)2 * T * S * R * 4 + 16;
+    if (smem > 227 * 1024) { wv_set_error("gemv: cols=%d needs %zu bytes of shared memory (max 232448)", b.cols, smem); return WV_ESHAPE; }
+    auto kern = gemv_chunked_kernel<F, R, S, D>;
+    if (!(attr_mask & (1u << dev))) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return WV_ECUDA;
+      attr_mask |= 1u << dev;
+    }
+    kern<<<dim3(grid, batch), WV_GEMV_THREADS, smem, st>>>(b, dx, dy, rb, re);
+    return cudaGetLastError() == cudaSuccess ? WV_OK : WV_ECUDA;
+  } else {
+    constexpr int NREC = QCfg<F>::INT_MID ? 9 : 7;
+    const size_t smem = (size_t)NREC * XS * 16 + (size_t)2 * T * S * R * 4 + 16;
+    if (smem > 227 * 1024) { wv_set_error("gemv: cols=%d needs %zu bytes of shared memory (max 232448)", b.cols, smem); return WV_ESHAPE; }
+    auto kern = gemv_idot_kernel<F, R, S, D>;
+    if (!(attr_mask & (1u << dev))) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return WV_ECUDA;
+      attr_mask |= 1u << dev;
+    }
+    uint4* xq = scratch_take((size_t)batch * 9 * XS * 16);
+    if (!xq) { wv_set_error("gemv: activation scratch too small for batch=%d cols=%d", batch, b.cols); return WV_ENOMEM; }
+    int rc = launch_xquant<fi.bits_lo>(dx, b.cols, batch, QCfg<F>::INT_MID ? fi.mid : 0, xq, st);
+    if (rc) return rc;
+    cudaError_t e = launch_pdl(kern, dim3(grid, batch), dim3(WV_GEMV_THREADS), smem, st, b, (const uint4*)xq, dy, rb, re);
+    if (e != cudaSuccess) { wv_set_error("gemv launch: %s", cudaGetErrorString(e)); return WV_ECUDA; }
+    return WV_OK;
+  }
 }
 
 template <int F>
 static int launch_format(const WvDevBlob& b, const float* dx, float* dy, int batch, int rb, int re, cudaStream_t st) {
-  // Default shape heuristic: few long rows -> split columns over 2 warps; many short rows -> 4 rows per warp.
   int R = g_tune_r, S = g_tune_s, D = g_tune_d;
-  const int nrows = re - rb;
-  const long long warp_slots = (long long)sm_count() * (WV_GEMV_THREADS / 32);
-  if (!R) R = (nrows / 4 >= warp_slots / 2) ? 4 : 2;
-  if (!S) S = (nrows / R < warp_slots / 2 && (b.cols >> 5) >= 64) ? 2 : 1;
+  constexpr WvFmtInfo fi = wv_fmt_info(F);
+  if (!R) R = (fi.table || fi.bits_lo == 8) ? 2 : 4;   // 8-bit planes: 4 rows of fragments would spill
+  if (!S) S = fi.table ? 1 : 2;
   if (!D) D = 2;
 #define WV_CASE(r, s, d) if (R == r && S == s && D == d) return launch_chunked<F, r, s, d>(b, dx, dy, batch, rb, re, st);
-  WV_CASE(2, 1, 2) WV_CASE(2, 2, 2) WV_CASE(4, 1, 2) WV_CASE(4, 2, 2)
-  WV_CASE(2, 1, 4) WV_CASE(2, 2, 4) WV_CASE(1, 2, 4) WV_CASE(1, 4, 4)
+  WV_CASE(2, 1, 2) WV_CASE(2, 2, 2) WV_CASE(2, 1, 4) WV_CASE(2, 2, 4) WV_CASE(4, 1, 2) WV_CASE(4, 2, 2) WV_CASE(2, 4, 2) WV_CASE(1, 1, 4)
 #undef WV_CASE
   return launch_chunked<F, 2, 1, 2>(b, dx, dy, batch, rb, re, st);
 }

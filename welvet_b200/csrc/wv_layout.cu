@@ -86,7 +86,11 @@ __global__ void relayout_kernel(WvDevBlob b, const uint8_t* __restrict__ raw, si
       float2* kd = reinterpret_cast<float2*>(const_cast<float*>(b.p0));
       kd[sb] = ok ? make_float2(read_f32(raw + off), read_f32(raw + off + 4)) : make_float2(1.f, 0.f);
     }
-    unsigned s0 = ok ? raw[off + 8 + 2 * cc] : 0, s1 = ok ? raw[off + 8 + 2 * cc + 1] : 0;
+    // A zero scale byte decodes as d/255 (kquant.go:180-182), which is exactly what byte 1
+    // decodes to (d*1/255), so it is stored as 1 and the GEMV needs no special case.
+    unsigned s0 = ok ? raw[off + 8 + 2 * cc] : 1, s1 = ok ? raw[off + 8 + 2 * cc + 1] : 1;
+    if (s0 == 0) s0 = 1;
+    if (s1 == 0) s1 = 1;
     if (fi.has_min) {
       unsigned m0 = ok ? raw[off + 24 + 2 * cc] : 0, m1 = ok ? raw[off + 24 + 2 * cc + 1] : 0;
       const_cast<uint32_t*>(b.km)[ch] = s0 | (s1 << 8) | (m0 << 16) | (m1 << 24);
