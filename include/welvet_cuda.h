@@ -100,9 +100,16 @@ int wv_pack(int format, int dtype, int block_weights, const float* w, int rows, 
 int wv_pack_upload_dev(uint64_t key, int format, int dtype, int block_weights, const float* d_w,
                        int rows, int cols, void* stream);
 
+/* After the caller has synchronised its stream: 0, or WV_ETIMEOUT when a bounded device wait
+ * of an asynchronous call (wv_matvec_dev) ran out since the last query. The reference reports
+ * device failures through the error of the synchronous call (webgpu/affine_cache.go:439-443). */
+int wv_device_status(void);
+
 /* Experiment hook: override rows-per-warp / column split / prefetch depth / grid size of the
  * chunked GEMV (0 = built-in choice). Not part of the reference surface. */
 void wv_set_tuning(int rows_per_warp, int col_split, int depth, int grid);
+/* Same for the TMA-fed kernel: rows per row group per tile (1, 2, 4) and ring depth cap. */
+void wv_set_tma_tuning(int rows_per_group, int stages);
 
 #ifdef __cplusplus
 }

@@ -17,7 +17,7 @@ SYMBOLS = [
     "wv_blob_upload", "wv_blob_upload_wire", "wv_blob_upload_shard", "wv_shard_range",
     "wv_blob_has", "wv_blob_evict", "wv_cache_clear", "wv_cache_bytes", "wv_cache_set_limit",
     "wv_blob_info", "wv_matvec", "wv_matvec_dev", "wv_unpack", "wv_unpack_dev",
-    "wv_pack_sizes", "wv_pack", "wv_pack_upload_dev", "wv_set_tuning",
+    "wv_pack_sizes", "wv_pack", "wv_pack_upload_dev", "wv_set_tuning", "wv_set_tma_tuning", "wv_device_status",
 ]
 
 WV_OK, WV_ESHAPE, WV_EFORMAT, WV_ENOMEM, WV_ECUDA, WV_ETIMEOUT, WV_ENOTFOUND, WV_EINIT, WV_EARG = (
@@ -53,6 +53,8 @@ def lib() -> C.CDLL:
         L.wv_cache_set_limit.argtypes = [u64]
         L.wv_set_tuning.restype = None
         L.wv_set_tuning.argtypes = [i, i, i, i]
+        L.wv_set_tma_tuning.restype = None
+        L.wv_set_tma_tuning.argtypes = [i, i]
         L.wv_init.argtypes = [i]
         L.wv_blob_upload.argtypes = [u64, i, i, i, i, i, vp, sz, vp, sz, vp, sz]
         L.wv_blob_upload_wire.argtypes = [u64, i, i, i, i, vp, sz]

@@ -19,11 +19,12 @@ LIB = os.path.join(HERE, "libwelvet_cuda.so")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
-COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-I", INCLUDE]
+COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-I", INCLUDE] + os.environ.get("WV_NVCC_EXTRA", "").split()
 SOURCES = {
     "wv_layout.cu": ["--fmad=false"],
     "wv_pack.cu": ["--fmad=false"],
     "wv_gemv.cu": [],
+    "wv_gemv_tma.cu": [],
     "wv_api.cu": [],
 }
 

@@ -30,6 +30,8 @@ extern "C" const char* wv_last_error(void) { return t_err; }
 
 // ---------------------------------------------------------------- session
 int wv_gemv_scratch_init(size_t bytes);  // wv_gemv.cu
+int wv_tma_init();                       // wv_gemv_tma.cu
+int wv_tma_take_error();
 struct Entry {
   WvDevBlob blob;
   void* mem = nullptr;
@@ -74,6 +76,7 @@ extern "C" int wv_init(int device) {
     if (const char* e = getenv("WELVET_CUDA_SCRATCH_MB")) { long v = atol(e); if (v > 0) mb = (size_t)v; }
     if (wv_gemv_scratch_init(mb << 20) != WV_OK) { wv_set_error("wv_init: cannot allocate %zu MB of activation scratch", mb); return WV_ENOMEM; }
   }
+  if (wv_tma_init() != WV_OK) { wv_set_error("wv_init: cannot allocate the device status word"); return WV_ENOMEM; }
   g_device = device;
   return WV_OK;
 }
@@ -410,7 +413,13 @@ extern "C" int wv_matvec(uint64_t key, const float* x, float* y, int batch, int 
   if (rc) { wv_set_error("wv_matvec: launch failed (%d): %s", rc, cudaGetErrorString(cudaGetLastError())); return rc; }
   CUDA_TRY(cudaMemcpyAsync(g_hy, g_dy, ny * 4, cudaMemcpyDeviceToHost, g_stream));
   CUDA_TRY(cudaStreamSynchronize(g_stream));
+  if (int te = wv_tma_take_error()) { wv_set_error("wv_matvec: a bounded device wait ran out (code %d)", te); return WV_ETIMEOUT; }
   memcpy(y, g_hy, ny * 4);
+  return WV_OK;
+}
+
+extern "C" int wv_device_status(void) {
+  if (int te = wv_tma_take_error()) { wv_set_error("a bounded device wait ran out (code %d)", te); return WV_ETIMEOUT; }
   return WV_OK;
 }
 

@@ -13,140 +13,11 @@
 //     products accumulate in f32 with packed f32x2 FMAs; asymmetric formats use the
 //     reference's own factorisation sc*sum(q*x) + mn*sum(x) (simd/dot_k.go:44-53);
 //   * warp-shuffle reduction, one store per row.
-#include "wv_common.cuh"
-#include <cuda_fp16.h>
-#include <cuda_runtime.h>
+#include "wv_gemv_common.cuh"
 
 #ifndef WV_GEMV_THREADS
 #define WV_GEMV_THREADS 512
 #endif
-
-__constant__ float c_grid4nl[16] = WV_IQ4NL_GRID;
-
-// ------------------------------------------------------------------ fragments
-template <int F> struct FragT {
-  static constexpr WvFmtInfo fi = wv_fmt_info(F);
-  static constexpr int BL = fi.bits_lo, BH = fi.bits_hi;
-  // number of 32-bit parameter registers per chunk-row
-  static constexpr int NP =
-      fi.kind == WK_KQUANT ? 3 : ((fi.has_min || fi.pgroup == 16) ? 2 : 1);
-  uint32_t lo[BL];
-  uint32_t hi[BH ? BH : 1];
-  uint32_t pr[NP];
-};
-
-template <int N> __device__ __forceinline__ void ldg_words(uint32_t (&dst)[N], const uint32_t* p) {
-  if constexpr (N == 1) { dst[0] = __ldg(p); }
-  else if constexpr (N == 2) { uint2 v = __ldg(reinterpret_cast<const uint2*>(p)); dst[0] = v.x; dst[1] = v.y; }
-  else if constexpr (N == 4) { uint4 v = __ldg(reinterpret_cast<const uint4*>(p)); dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w; }
-  else if constexpr (N == 8) {
-    uint4 v = __ldg(reinterpret_cast<const uint4*>(p)), u = __ldg(reinterpret_cast<const uint4*>(p) + 1);
-    dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w; dst[4] = u.x; dst[5] = u.y; dst[6] = u.z; dst[7] = u.w;
-  }
-}
-
-// cg = global chunk index (row * chunks_per_row + chunk)
-template <int F> __device__ __forceinline__ void load_frag(FragT<F>& f, const WvDevBlob& b, long long cg) {
-  constexpr WvFmtInfo fi = wv_fmt_info(F);
-  ldg_words<FragT<F>::BL>(f.lo, b.lo + cg * FragT<F>::BL);
-  if constexpr (fi.bits_hi == 1) f.hi[0] = __ldg(b.hi + cg);
-  if constexpr (fi.bits_hi == 2) { uint2 v = __ldg(reinterpret_cast<const uint2*>(b.hi) + cg); f.hi[0] = v.x; f.hi[1] = v.y; }
-  if constexpr (fi.kind == WK_KQUANT) {
-    float2 dd = __ldg(reinterpret_cast<const float2*>(b.p0) + (cg >> 3));
-    f.pr[0] = __float_as_uint(dd.x); f.pr[1] = __float_as_uint(dd.y);
-    if constexpr (fi.has_min) f.pr[2] = __ldg(b.km + cg);
-    else f.pr[2] = __ldg(reinterpret_cast<const unsigned short*>(b.km) + cg);
-  } else if constexpr (fi.kind == WK_CLASSIC) {
-    f.pr[0] = __float_as_uint(__ldg(b.p0 + cg));
-    if constexpr (fi.has_min) f.pr[1] = __float_as_uint(__ldg(b.p1 + cg));
-  } else if constexpr (fi.kind == WK_BINARY) {
-    f.pr[0] = __float_as_uint(__ldg(b.p0 + (cg * 32) / b.group));
-  } else if constexpr (fi.kind == WK_AFFINE) {
-    long long g = (cg * 32) / b.group;
-    f.pr[0] = __float_as_uint(__ldg(b.p0 + g)); f.pr[1] = __float_as_uint(__ldg(b.p1 + g));
-  } else if constexpr (fi.pgroup == 16) {  // IQ *_XS/_S, ternary: two scales per chunk
-    float2 s = __ldg(reinterpret_cast<const float2*>(b.p0) + cg);
-    f.pr[0] = __float_as_uint(s.x); f.pr[1] = __float_as_uint(s.y);
-  } else {  // IQ with one scale per 32
-    f.pr[0] = __float_as_uint(__ldg(b.p0 + cg));
-  }
-}
-
-// ------------------------------------------------------------------ chunk dot
-// s0 / s1 = sum over the first / second 16 weights of (code - MID) * x (1-bit planes put
-// everything in s0). xr[k] holds the four activations matching byte lanes 0..3 of group k.
-template <int F>
-__device__ __forceinline__ void chunk_dot(const FragT<F>& f, const float4 (&xr)[8], const float* tbl, float& s0, float& s1) {
-  constexpr WvFmtInfo fi = wv_fmt_info(F);
-  constexpr int BL = fi.bits_lo, BH = fi.bits_hi, SPW = 8 / BL;
-  constexpr unsigned MASK = 0x01010101u * ((1u << BL) - 1u);
-  constexpr unsigned MASKH = BH ? (0x01010101u * ((1u << BH) - 1u)) << BL : 0u;
-  const float magic = 8388608.0f + (float)fi.mid;
-  float2 a0 = make_float2(0.f, 0.f), a1 = a0, b0 = a0, b1 = a0;
-#pragma unroll
-  for (int k = 0; k < 8; k++) {
-    const int w = k / SPW, s = k % SPW;
-    unsigned bytes = (f.lo[w] >> (BL * s)) & MASK;
-    if constexpr (BH > 0) {
-      const int hw = (k * BH) >> 3, sh = (k * BH) & 7;
-      unsigned hv = f.hi[hw];
-      hv = sh >= BL ? (hv >> (sh - BL)) : (hv << (BL - sh));
-      bytes |= hv & MASKH;
-    }
-    float2 q01, q23;
-    if constexpr (fi.table) {
-      q01.x = tbl[(bytes & 0xffu) * 32]; q01.y = tbl[((bytes >> 8) & 0xffu) * 32];
-      q23.x = tbl[((bytes >> 16) & 0xffu) * 32]; q23.y = tbl[(bytes >> 24) * 32];
-    } else {
-      q01.x = __uint_as_float(__byte_perm(bytes, 0x4B000000u, 0x7650)) - magic;
-      q01.y = __uint_as_float(__byte_perm(bytes, 0x4B000000u, 0x7651)) - magic;
-      q23.x = __uint_as_float(__byte_perm(bytes, 0x4B000000u, 0x7652)) - magic;
-      q23.y = __uint_as_float(__byte_perm(bytes, 0x4B000000u, 0x7653)) - magic;
-    }
-    const float2 x01 = make_float2(xr[k].x, xr[k].y), x23 = make_float2(xr[k].z, xr[k].w);
-    if (BL == 1 || k < 4) { a0 = __ffma2_rn(q01, x01, a0); a1 = __ffma2_rn(q23, x23, a1); }
-    else { b0 = __ffma2_rn(q01, x01, b0); b1 = __ffma2_rn(q23, x23, b1); }
-  }
-  s0 = (a0.x + a0.y) + (a1.x + a1.y);
-  s1 = (b0.x + b0.y) + (b1.x + b1.y);
-}
-
-__device__ __forceinline__ float u8f(unsigned v, int byte) {
-  return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7650 + byte)) - 8388608.0f;
-}
-
-// Contribution of one chunk-row to its output row.
-template <int F>
-__device__ __forceinline__ float chunk_value(const FragT<F>& f, const float4 (&xr)[8], float2 sx, const float* tbl) {
-  constexpr WvFmtInfo fi = wv_fmt_info(F);
-  float s0, s1;
-  chunk_dot<F>(f, xr, tbl, s0, s1);
-  if constexpr (fi.kind == WK_KQUANT) {
-    const float d = __uint_as_float(f.pr[0]) * (1.0f / 255.0f);
-    float a0 = d * u8f(f.pr[2], 0), a1 = d * u8f(f.pr[2], 1);
-    if (a0 == 0.0f) a0 = d;  // kquant.go:180-182: a zero group scale decodes as d/255
-    if (a1 == 0.0f) a1 = d;
-    float v = a0 * s0 + a1 * s1;
-    if constexpr (fi.has_min) {
-      const float dm = __uint_as_float(f.pr[1]) * (1.0f / 127.0f);
-      const unsigned mb = f.pr[2] ^ 0x80800000u;  // int8 -> biased uint8
-      v += dm * ((u8f(mb, 2) - 128.0f) * sx.x + (u8f(mb, 3) - 128.0f) * sx.y);
-    }
-    return v;
-  } else if constexpr (fi.kind == WK_CLASSIC || fi.kind == WK_AFFINE) {
-    float v = __uint_as_float(f.pr[0]) * (s0 + s1);
-    if constexpr (fi.has_min) v += __uint_as_float(f.pr[1]) * (sx.x + sx.y);
-    return v;
-  } else if constexpr (fi.kind == WK_BINARY || (fi.kind == WK_IQ && fi.sign)) {
-    return __uint_as_float(f.pr[0]) * (2.0f * s0 - (sx.x + sx.y));
-  } else if constexpr (fi.kind == WK_TERNARY) {
-    return __uint_as_float(f.pr[0]) * s0 + __uint_as_float(f.pr[1]) * s1;
-  } else {  // IQ linear / table
-    if constexpr (fi.half_mid) { s0 -= 0.5f * sx.x; s1 -= 0.5f * sx.y; }
-    if constexpr (fi.pgroup == 16) return __uint_as_float(f.pr[0]) * s0 + __uint_as_float(f.pr[1]) * s1;
-    else return __uint_as_float(f.pr[0]) * (s0 + s1);
-  }
-}
 
 // ------------------------------------------------------------------ shared-memory x
 // x permutation for lo-plane width B: column 32c + j lives at float ((k*XS + c)*4 + m).
@@ -274,37 +145,7 @@ gemv_chunked_kernel(const WvDevBlob b, const float* __restrict__ x, float* __res
   }
 }
 
-// ------------------------------------------------------------------ integer-dot kernel
-// The f32 path above spends ~6 instructions per weight (byte permute, subtract, FMA, ...) and
-// is issue-bound far below HBM speed. Every format except IQ4_NL has small integer codes, so
-// the hot loop here is integer: activations are converted once per call into block fixed
-// point (per 32 columns: X_j = rint(x_j * 2^(22-e)), 2^e > max|x| of the block, |X_j| <= 2^22,
-// split into three byte limbs X = L0 + 256 L1 + 65536 L2 packed as int8x4 words in code-group
-// order) and each group of four codes meets its four activations in one dp4a per limb:
-// 0.75 dp4a per weight with exact integer accumulation. The limb sums are recombined in f32
-// and scaled by 2^(e-22) and the block's scale.
-//   error: |x_j - X_j 2^(e-22)| <= 2^(e-23), i.e. 2^-23 of the 32-column block maximum per
-//   element (f32's own rounding is 2^-24 of the element), and no rounding inside the dot;
-//   symmetric formats subtract mid in the integer domain (accumulators start at -mid*sum(L)),
-//   so all-zero weights give exactly 0.
-__device__ __forceinline__ int dp4a_uu(unsigned a, unsigned b, int c) {
-  int d;
-  asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
-}
-__device__ __forceinline__ int dp4a_us(unsigned a, unsigned b, int c) {
-  int d;
-  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
-}
-
-template <int F> struct QCfg {
-  static constexpr WvFmtInfo fi = wv_fmt_info(F);
-  static constexpr bool HALVES = fi.pgroup == 16;                 // two parameter groups per chunk
-  static constexpr bool INT_MID = fi.mid != 0 && !fi.half_mid;    // exact integer offset
-  static constexpr int NH = HALVES ? 2 : 1;
-};
-
+// ------------------------------------------------------------------ activation pre-quantisation
 // Activation record, identical in the global scratch written by xquant_kernel and in the
 // shared-memory copy every GEMV CTA makes of it (uint4 units, XS = chunks_per_row | 1):
 //   [0 , 6XS)   xq    24 int8x4 words per chunk, word t = limb*8 + k at uint4 (t>>2)*XS + c
@@ -360,25 +201,20 @@ __global__ void __launch_bounds__(128) xquant_kernel(const float* __restrict__ x
   o[8 * XS + c] = make_uint4((unsigned)(-imid * sl[2][0]), (unsigned)(-imid * sl[2][1]), 0u, 0u);
 }
 
+// ------------------------------------------------------------------ integer-dot kernel (register loads)
 // Work split: CTA b owns rows [n*b/grid, n*(b+1)/grid); inside the CTA, team t (S warps that
-// split the columns) owns an equal contiguous share of those rows and walks it R rows at a time.
+// split the columns) owns an equal contiguous share of those rows and walks it R rows at a
+// time, one 32-weight chunk per lane per step, D steps of weight loads in flight.
+// Used for shapes the TMA-fed kernel (wv_gemv_tma.cu) does not take.
 template <int F, int R, int S, int D>
 __global__ void __launch_bounds__(WV_GEMV_THREADS, 1)
 gemv_idot_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, float* __restrict__ y, int row_begin, int row_end) {
-  constexpr WvFmtInfo fi = wv_fmt_info(F);
-  constexpr int BL = fi.bits_lo, BH = fi.bits_hi, SPW = 8 / BL;
-  constexpr unsigned MASK = 0x01010101u * ((1u << BL) - 1u);
-  constexpr unsigned MASKH = BH ? (0x01010101u * ((1u << BH) - 1u)) << BL : 0u;
   constexpr int NW = WV_GEMV_THREADS / 32, T = NW / S;
-  constexpr bool HALVES = QCfg<F>::HALVES, INT_MID = QCfg<F>::INT_MID;
-  constexpr int NH = QCfg<F>::NH;
-  constexpr int NREC = INT_MID ? 9 : 7;
+  constexpr int NREC = QCfg<F>::NREC;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int cpr = b.cols >> 5;
   const int XS = cpr | 1;
-  uint4* xq = reinterpret_cast<uint4*>(smem_raw);                     // [6][XS]
-  const float4* meta = reinterpret_cast<const float4*>(xq + 6 * XS);  // [XS]
-  const int4* ini = reinterpret_cast<const int4*>(xq + 7 * XS);       // [2][XS]
+  uint4* xq = reinterpret_cast<uint4*>(smem_raw);
   float* team = reinterpret_cast<float*>(xq + NREC * XS);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int tm = warp / S, sid = warp % S;
@@ -432,79 +268,10 @@ gemv_idot_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, float* __rest
         issue(buf[d]);
         const int c = (cit * S + sid) * 32 + lane;
         if (c < cpr) {
-          unsigned xw[24];
+          XQRegs xr;
+          load_xq<F>(xr, xq, XS, c);
 #pragma unroll
-          for (int q = 0; q < 6; q++) {
-            const uint4 v = xq[q * XS + c];
-            xw[4 * q] = v.x; xw[4 * q + 1] = v.y; xw[4 * q + 2] = v.z; xw[4 * q + 3] = v.w;
-          }
-          const float4 mt = meta[c];
-          int iv[6] = {0, 0, 0, 0, 0, 0};
-          if constexpr (INT_MID) {
-            const int4 a = ini[c], bq = ini[XS + c];
-            iv[0] = a.x; iv[1] = a.y; iv[2] = a.z; iv[3] = a.w; iv[4] = bq.x; iv[5] = bq.y;
-            if constexpr (!HALVES) { iv[0] += iv[1]; iv[2] += iv[3]; iv[4] += iv[5]; }
-          }
-#pragma unroll
-          for (int r = 0; r < R; r++) {
-            const FragT<F>& f = cur[r];
-            int I[3][2];
-#pragma unroll
-            for (int l = 0; l < 3; l++) { I[l][0] = iv[l * 2]; I[l][1] = HALVES ? iv[l * 2 + 1] : 0; }
-#pragma unroll
-            for (int k = 0; k < 8; k++) {
-              const int w = k / SPW, sh = k % SPW;
-              unsigned bytes = (f.lo[w] >> (BL * sh)) & MASK;
-              if constexpr (BH > 0) {
-                const int hw = (k * BH) >> 3, hs = (k * BH) & 7;
-                unsigned hv = f.hi[hw];
-                hv = hs >= BL ? (hv >> (hs - BL)) : (hv << (BL - hs));
-                bytes |= hv & MASKH;
-              }
-              const int h = (HALVES && k >= 4) ? 1 : 0;  // first / second 16 weights of the chunk
-              I[0][h] = dp4a_uu(bytes, xw[k], I[0][h]);
-              I[1][h] = dp4a_uu(bytes, xw[8 + k], I[1][h]);
-              I[2][h] = dp4a_us(bytes, xw[16 + k], I[2][h]);
-            }
-            float val[2];
-#pragma unroll
-            for (int h = 0; h < NH; h++)
-              val[h] = fmaf(65536.0f, (float)I[2][h], (float)(I[0][h] + (I[1][h] << 8)));
-            float v;
-            if constexpr (fi.kind == WK_KQUANT) {
-              // scale bytes were remapped 0 -> 1 at upload (kquant.go:180-182: a zero group
-              // scale decodes as d/255), so no test is needed here
-              const float t = u8f(f.pr[2], 0) * val[0] + u8f(f.pr[2], 1) * val[1];
-              v = (__uint_as_float(f.pr[0]) * (1.0f / 255.0f)) * t;
-              if constexpr (fi.has_min) {
-                const unsigned mb = f.pr[2] ^ 0x80800000u;  // int8 -> biased uint8
-                const float mm = (__uint_as_float(__byte_perm(mb, 0x4B000000u, 0x7652)) - 8388736.0f) * mt.z +
-                                 (__uint_as_float(__byte_perm(mb, 0x4B000000u, 0x7653)) - 8388736.0f) * mt.w;
-                acc[r] = fmaf(__uint_as_float(f.pr[1]) * (1.0f / 127.0f), mm, acc[r]);
-              }
-              acc[r] = fmaf(mt.x, v, acc[r]);
-            } else {
-              if constexpr (fi.kind == WK_CLASSIC || fi.kind == WK_AFFINE) {
-                v = __uint_as_float(f.pr[0]) * val[0];
-                if constexpr (fi.has_min) acc[r] = fmaf(__uint_as_float(f.pr[1]), mt.y, acc[r]);
-              } else if constexpr (fi.kind == WK_TERNARY) {
-                v = __uint_as_float(f.pr[0]) * val[0] + __uint_as_float(f.pr[1]) * val[1];
-              } else if constexpr (fi.sign) {
-                v = __uint_as_float(f.pr[0]) * (2.0f * val[0]);
-                acc[r] = fmaf(-__uint_as_float(f.pr[0]), mt.y, acc[r]);
-              } else {  // IQ linear grids: (code - mid - 0.5)
-                constexpr float hm = (float)fi.mid + 0.5f;
-                if constexpr (HALVES) {
-                  v = __uint_as_float(f.pr[0]) * val[0] + __uint_as_float(f.pr[1]) * val[1];
-                  acc[r] -= hm * (__uint_as_float(f.pr[0]) * mt.z + __uint_as_float(f.pr[1]) * mt.w);
-                } else {
-                  v = __uint_as_float(f.pr[0]) * val[0];
-                  acc[r] = fmaf(-hm * __uint_as_float(f.pr[0]), mt.y, acc[r]);
-                }
-              }
-              acc[r] = fmaf(mt.x, v, acc[r]);
-            }
-          }
+          for (int r = 0; r < R; r++) acc[r] += idot_chunk<F>(cur[r], xr);
         }
         if (++cit == iters) {
 #pragma unroll
@@ -620,7 +387,9 @@ gemv_dense_kernel(const WvDevBlob b, const float* __restrict__ x, float* __restr
 int wv_launch_gemv_ragged(const WvDevBlob& b, const float* dx, float* dy, int batch, int row_begin, int row_end, cudaStream_t st);
 
 static int g_sm_count = 0;
-static int sm_count() {
+int wv_sm_count();
+static int sm_count() { return wv_sm_count(); }
+int wv_sm_count() {
   if (!g_sm_count) {
     int dev = 0; cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
@@ -644,7 +413,7 @@ int wv_gemv_scratch_init(size_t bytes) {
   g_xq_bytes = bytes; g_xq_head = 0;
   return WV_OK;
 }
-static uint4* scratch_take(size_t bytes) {
+uint4* wv_scratch_take(size_t bytes) {
   bytes = (bytes + 255) & ~(size_t)255;
   if (!g_xq_arena || bytes > g_xq_bytes) return nullptr;
   if (g_xq_head + bytes > g_xq_bytes) g_xq_head = 0;
@@ -653,22 +422,20 @@ static uint4* scratch_take(size_t bytes) {
   return p;
 }
 
-template <typename... KArgs, typename... Args>
-static cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
-  cudaLaunchAttribute at[1];
-  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  at[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = at; cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
-}
-
 template <int BL>
 static int launch_xquant(const float* dx, int cols, int batch, int imid, uint4* out, cudaStream_t st) {
   const int cpr = cols >> 5;
   cudaError_t e = launch_pdl(xquant_kernel<BL>, dim3((cpr + 127) / 128, batch), dim3(128), 0, st, dx, cols, imid, out);
   return e == cudaSuccess ? WV_OK : WV_ECUDA;
+}
+int wv_launch_xquant(int bits_lo, const float* dx, int cols, int batch, int imid, uint4* out, cudaStream_t st) {
+  switch (bits_lo) {
+  case 1: return launch_xquant<1>(dx, cols, batch, imid, out, st);
+  case 2: return launch_xquant<2>(dx, cols, batch, imid, out, st);
+  case 4: return launch_xquant<4>(dx, cols, batch, imid, out, st);
+  case 8: return launch_xquant<8>(dx, cols, batch, imid, out, st);
+  }
+  return WV_EFORMAT;
 }
 
 template <int F, int R, int S, int D>
@@ -701,7 +468,7 @@ static int launch_chunked(const WvDevBlob& b, const float* dx, float* dy, int ba
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return WV_ECUDA;
       attr_mask |= 1u << dev;
     }
-    uint4* xq = scratch_take((size_t)batch * 9 * XS * 16);
+    uint4* xq = wv_scratch_take((size_t)batch * 9 * XS * 16);
     if (!xq) { wv_set_error("gemv: activation scratch too small for batch=%d cols=%d", batch, b.cols); return WV_ENOMEM; }
     int rc = launch_xquant<fi.bits_lo>(dx, b.cols, batch, QCfg<F>::INT_MID ? fi.mid : 0, xq, st);
     if (rc) return rc;
@@ -745,6 +512,10 @@ static int launch_dense(const WvDevBlob& b, const float* dx, float* dy, int batc
 int wv_launch_gemv(const WvDevBlob& b, const float* dx, float* dy, int batch, int row_begin, int row_end, cudaStream_t st) {
   if (row_end <= row_begin || batch <= 0) return WV_OK;
   if (!b.fast) return wv_launch_gemv_ragged(b, dx, dy, batch, row_begin, row_end, st);
+  if (b.format != WV_NONE && !g_tune_r) {   // an explicit tuning override selects the register-load kernels
+    const int rc = wv_launch_gemv_tma(b, dx, dy, batch, row_begin, row_end, st);
+    if (rc != 1) return rc;
+  }
   switch (b.format) {
   case WV_NONE:
     if (b.dtype == WV_DT_F32) return launch_dense<WV_DT_F32>(b, dx, dy, batch, row_begin, row_end, st);

@@ -1,0 +1,340 @@
+// Device helpers shared by the GEMV kernels: per-chunk weight fragments, the f32 chunk math
+// (IQ4_NL) and the integer-dot chunk math (every other packed format).
+#pragma once
+#include "wv_common.cuh"
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+static __constant__ float c_grid4nl[16] = WV_IQ4NL_GRID;
+
+// ------------------------------------------------------------------ fragments
+template <int F> struct FragT {
+  static constexpr WvFmtInfo fi = wv_fmt_info(F);
+  static constexpr int BL = fi.bits_lo, BH = fi.bits_hi;
+  // number of 32-bit parameter registers per chunk-row
+  static constexpr int NP =
+      fi.kind == WK_KQUANT ? 3 : ((fi.has_min || fi.pgroup == 16) ? 2 : 1);
+  uint32_t lo[BL];
+  uint32_t hi[BH ? BH : 1];
+  uint32_t pr[NP];
+};
+
+template <int N> __device__ __forceinline__ void ldg_words(uint32_t (&dst)[N], const uint32_t* p) {
+  if constexpr (N == 1) { dst[0] = __ldg(p); }
+  else if constexpr (N == 2) { uint2 v = __ldg(reinterpret_cast<const uint2*>(p)); dst[0] = v.x; dst[1] = v.y; }
+  else if constexpr (N == 4) { uint4 v = __ldg(reinterpret_cast<const uint4*>(p)); dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w; }
+  else if constexpr (N == 8) {
+    uint4 v = __ldg(reinterpret_cast<const uint4*>(p)), u = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+    dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w; dst[4] = u.x; dst[5] = u.y; dst[6] = u.z; dst[7] = u.w;
+  }
+}
+
+// cg = global chunk index (row * chunks_per_row + chunk)
+template <int F> __device__ __forceinline__ void load_frag(FragT<F>& f, const WvDevBlob& b, long long cg) {
+  constexpr WvFmtInfo fi = wv_fmt_info(F);
+  ldg_words<FragT<F>::BL>(f.lo, b.lo + cg * FragT<F>::BL);
+  if constexpr (fi.bits_hi == 1) f.hi[0] = __ldg(b.hi + cg);
+  if constexpr (fi.bits_hi == 2) { uint2 v = __ldg(reinterpret_cast<const uint2*>(b.hi) + cg); f.hi[0] = v.x; f.hi[1] = v.y; }
+  if constexpr (fi.kind == WK_KQUANT) {
+    float2 dd = __ldg(reinterpret_cast<const float2*>(b.p0) + (cg >> 3));
+    f.pr[0] = __float_as_uint(dd.x); f.pr[1] = __float_as_uint(dd.y);
+    if constexpr (fi.has_min) f.pr[2] = __ldg(b.km + cg);
+    else f.pr[2] = __ldg(reinterpret_cast<const unsigned short*>(b.km) + cg);
+  } else if constexpr (fi.kind == WK_CLASSIC) {
+    f.pr[0] = __float_as_uint(__ldg(b.p0 + cg));
+    if constexpr (fi.has_min) f.pr[1] = __float_as_uint(__ldg(b.p1 + cg));
+  } else if constexpr (fi.kind == WK_BINARY) {
+    f.pr[0] = __float_as_uint(__ldg(b.p0 + (cg * 32) / b.group));
+  } else if constexpr (fi.kind == WK_AFFINE) {
+    long long g = (cg * 32) / b.group;
+    f.pr[0] = __float_as_uint(__ldg(b.p0 + g)); f.pr[1] = __float_as_uint(__ldg(b.p1 + g));
+  } else if constexpr (fi.pgroup == 16) {  // IQ *_XS/_S, ternary: two scales per chunk
+    float2 s = __ldg(reinterpret_cast<const float2*>(b.p0) + cg);
+    f.pr[0] = __float_as_uint(s.x); f.pr[1] = __float_as_uint(s.y);
+  } else {  // IQ with one scale per 32
+    f.pr[0] = __float_as_uint(__ldg(b.p0 + cg));
+  }
+}
+
+// ------------------------------------------------------------------ chunk dot
+// s0 / s1 = sum over the first / second 16 weights of (code - MID) * x (1-bit planes put
+// everything in s0). xr[k] holds the four activations matching byte lanes 0..3 of group k.
+template <int F>
+__device__ __forceinline__ void chunk_dot(const FragT<F>& f, const float4 (&xr)[8], const float* tbl, float& s0, float& s1) {
+  constexpr WvFmtInfo fi = wv_fmt_info(F);
+  constexpr int BL = fi.bits_lo, BH = fi.bits_hi, SPW = 8 / BL;
+  constexpr unsigned MASK = 0x01010101u * ((1u << BL) - 1u);
+  constexpr unsigned MASKH = BH ? (0x01010101u * ((1u << BH) - 1u)) << BL : 0u;
+  const float magic = 8388608.0f + (float)fi.mid;
+  float2 a0 = make_float2(0.f, 0.f), a1 = a0, b0 = a0, b1 = a0;
+#pragma unroll
+  for (int k = 0; k < 8; k++) {
+    const int w = k / SPW, s = k % SPW;
+    unsigned bytes = (f.lo[w] >> (BL * s)) & MASK;
+    if constexpr (BH > 0) {
+      const int hw = (k * BH) >> 3, sh = (k * BH) & 7;
+      unsigned hv = f.hi[hw];
+      hv = sh >= BL ? (hv >> (sh - BL)) : (hv << (BL - sh));
+      bytes |= hv & MASKH;
+    }
+    float2 q01, q23;
+    if constexpr (fi.table) {
+      q01.x = tbl[(bytes & 0xffu) * 32]; q01.y = tbl[((bytes >> 8) & 0xffu) * 32];
+      q23.x = tbl[((bytes >> 16) & 0xffu) * 32]; q23.y = tbl[(bytes >> 24) * 32];
+    } else {
+      q01.x = __uint_as_float(__byte_perm(bytes, 0x4B000000u, 0x7650)) - magic;
+      q01.y = __uint_as_float(__byte_perm(bytes, 0x4B000000u, 0x7651)) - magic;
+      q23.x = __uint_as_float(__byte_perm(bytes, 0x4B000000u, 0x7652)) - magic;
+      q23.y = __uint_as_float(__byte_perm(bytes, 0x4B000000u, 0x7653)) - magic;
+    }
+    const float2 x01 = make_float2(xr[k].x, xr[k].y), x23 = make_float2(xr[k].z, xr[k].w);
+    if (BL == 1 || k < 4) { a0 = __ffma2_rn(q01, x01, a0); a1 = __ffma2_rn(q23, x23, a1); }
+    else { b0 = __ffma2_rn(q01, x01, b0); b1 = __ffma2_rn(q23, x23, b1); }
+  }
+  s0 = (a0.x + a0.y) + (a1.x + a1.y);
+  s1 = (b0.x + b0.y) + (b1.x + b1.y);
+}
+
+__device__ __forceinline__ float u8f(unsigned v, int byte) {
+  return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7650 + byte)) - 8388608.0f;
+}
+
+// Contribution of one chunk-row to its output row.
+template <int F>
+__device__ __forceinline__ float chunk_value(const FragT<F>& f, const float4 (&xr)[8], float2 sx, const float* tbl) {
+  constexpr WvFmtInfo fi = wv_fmt_info(F);
+  float s0, s1;
+  chunk_dot<F>(f, xr, tbl, s0, s1);
+  if constexpr (fi.kind == WK_KQUANT) {
+    const float d = __uint_as_float(f.pr[0]) * (1.0f / 255.0f);
+    float a0 = d * u8f(f.pr[2], 0), a1 = d * u8f(f.pr[2], 1);
+    if (a0 == 0.0f) a0 = d;  // kquant.go:180-182: a zero group scale decodes as d/255
+    if (a1 == 0.0f) a1 = d;
+    float v = a0 * s0 + a1 * s1;
+    if constexpr (fi.has_min) {
+      const float dm = __uint_as_float(f.pr[1]) * (1.0f / 127.0f);
+      const unsigned mb = f.pr[2] ^ 0x80800000u;  // int8 -> biased uint8
+      v += dm * ((u8f(mb, 2) - 128.0f) * sx.x + (u8f(mb, 3) - 128.0f) * sx.y);
+    }
+    return v;
+  } else if constexpr (fi.kind == WK_CLASSIC || fi.kind == WK_AFFINE) {
+    float v = __uint_as_float(f.pr[0]) * (s0 + s1);
+    if constexpr (fi.has_min) v += __uint_as_float(f.pr[1]) * (sx.x + sx.y);
+    return v;
+  } else if constexpr (fi.kind == WK_BINARY || (fi.kind == WK_IQ && fi.sign)) {
+    return __uint_as_float(f.pr[0]) * (2.0f * s0 - (sx.x + sx.y));
+  } else if constexpr (fi.kind == WK_TERNARY) {
+    return __uint_as_float(f.pr[0]) * s0 + __uint_as_float(f.pr[1]) * s1;
+  } else {  // IQ linear / table
+    if constexpr (fi.half_mid) { s0 -= 0.5f * sx.x; s1 -= 0.5f * sx.y; }
+    if constexpr (fi.pgroup == 16) return __uint_as_float(f.pr[0]) * s0 + __uint_as_float(f.pr[1]) * s1;
+    else return __uint_as_float(f.pr[0]) * (s0 + s1);
+  }
+}
+
+
+// ------------------------------------------------------------------ integer-dot chunk math
+// Activations arrive as block fixed point (see xquant_kernel): per 32 columns
+// X_j = rint(x_j * 2^(22-e)), 2^e > max|x| of the block, split into three byte limbs
+// X = L0 + 256 L1 + 65536 L2 packed as int8x4 words in code-group order. Each group of four
+// codes meets its four activations in one dp4a per limb (0.75 dp4a per weight, exact integer
+// accumulation); the limb sums are recombined in f32 and scaled by sf = 2^(e-22) and the
+// block's scale. Per element |x_j - X_j sf| <= 2^-23 of the block maximum (f32's own rounding
+// is 2^-24 of the element) and there is no rounding inside the dot. Symmetric formats subtract
+// mid in the integer domain (accumulators start at -mid*sum(L)): all-zero weights give exactly 0.
+__device__ __forceinline__ int dp4a_uu(unsigned a, unsigned b, int c) {
+  int d;
+  asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ int dp4a_us(unsigned a, unsigned b, int c) {
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+template <int F> struct QCfg {
+  static constexpr WvFmtInfo fi = wv_fmt_info(F);
+  static constexpr bool HALVES = fi.pgroup == 16;                 // two parameter groups per chunk
+  static constexpr bool INT_MID = fi.mid != 0 && !fi.half_mid;    // exact integer offset
+  static constexpr int NH = HALVES ? 2 : 1;
+  static constexpr int NREC = INT_MID ? 9 : 7;                    // uint4 records per chunk actually read
+};
+
+// One chunk's activation record held in registers.
+struct XQRegs {
+  unsigned xw[24];   // word limb*8 + k
+  float4 mt;         // {sf, sf*SX(all), sf*SX(first 16), sf*SX(second 16)}
+  int iv[6];         // -mid*sum(limb l, half h) at l*2+h (halves pre-added for 32-wide groups)
+};
+
+// Record layout in memory (uint4 units, XS = chunks_per_row | 1), see xquant_kernel:
+// [0,6XS) xq, [6XS,7XS) meta, [7XS,9XS) ini.
+template <int F, typename P>
+__device__ __forceinline__ void load_xq(XQRegs& x, const P* rec, int XS, int c) {
+#pragma unroll
+  for (int q = 0; q < 6; q++) {
+    const uint4 v = rec[q * XS + c];
+    x.xw[4 * q] = v.x; x.xw[4 * q + 1] = v.y; x.xw[4 * q + 2] = v.z; x.xw[4 * q + 3] = v.w;
+  }
+  const uint4 m = rec[6 * XS + c];
+  x.mt = make_float4(__uint_as_float(m.x), __uint_as_float(m.y), __uint_as_float(m.z), __uint_as_float(m.w));
+#pragma unroll
+  for (int i = 0; i < 6; i++) x.iv[i] = 0;
+  if constexpr (QCfg<F>::INT_MID) {
+    const uint4 a = rec[7 * XS + c], bq = rec[8 * XS + c];
+    x.iv[0] = (int)a.x; x.iv[1] = (int)a.y; x.iv[2] = (int)a.z; x.iv[3] = (int)a.w; x.iv[4] = (int)bq.x; x.iv[5] = (int)bq.y;
+    if constexpr (!QCfg<F>::HALVES) { x.iv[0] += x.iv[1]; x.iv[2] += x.iv[3]; x.iv[4] += x.iv[5]; }
+  }
+}
+
+__device__ __forceinline__ int dp4a_su(unsigned a, unsigned b, int c) {
+  int d;
+  asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+// Block-fixed-point conversion of one 32-column chunk straight into registers (what
+// xquant_kernel writes to memory for the register-load kernels). xc points at the chunk's 32
+// floats in shared memory. It runs once per kernel, so it is written as rolled loops over the
+// eight code groups (code that executes once must stay small); the 24 words pass through a
+// per-thread local array and are then copied to registers with static indices.
+template <int F>
+__device__ __forceinline__ void quantize_chunk(XQRegs& x, const float* xc) {
+  constexpr WvFmtInfo fi = wv_fmt_info(F);
+  constexpr int BL = fi.bits_lo, CPW = 32 / BL, SPW = 8 / BL;
+  float amax = 0.f, probe = 0.f;
+#pragma unroll 4
+  for (int j = 0; j < 32; j++) { const float v = xc[j]; amax = fmaxf(amax, fabsf(v)); probe = fmaf(v, 0.f, probe); }
+  const unsigned eb = (__float_as_uint(amax) >> 23) & 0xffu;
+  float sf = 0.f, inv = 0.f;
+  if (probe != 0.f || eb == 255u) sf = __uint_as_float(0x7fc00000u);  // inf / NaN in x: results become NaN
+  else if (eb >= 22u) { sf = __uint_as_float((eb - 21u) << 23); inv = __uint_as_float((275u - eb) << 23); }
+  unsigned tmp[24];
+  int sl[3][2] = {{0, 0}, {0, 0}, {0, 0}};
+#pragma unroll
+  for (int half = 0; half < 2; half++) {
+    // 1-bit planes split the halves by byte lane instead of by group; they never need the
+    // per-half sums, so everything is accumulated into sl[.][0] for them.
+#pragma unroll 1
+    for (int k = half * 4; k < half * 4 + 4; k++) {
+      const float* p = xc + (k / SPW) * CPW + (k % SPW);   // column of byte lane 0; lane m adds m*SPW
+      // round to nearest integer through the mantissa of 1.5*2^23 + v (|v| <= 2^22): full-rate
+      // FMA + integer subtract instead of the quarter-rate float-to-int conversion
+      const int X0 = __float_as_int(fmaf(p[0], inv, 12582912.0f)) - 0x4B400000, X1 = __float_as_int(fmaf(p[SPW], inv, 12582912.0f)) - 0x4B400000;
+      const int X2 = __float_as_int(fmaf(p[2 * SPW], inv, 12582912.0f)) - 0x4B400000, X3 = __float_as_int(fmaf(p[3 * SPW], inv, 12582912.0f)) - 0x4B400000;
+      const unsigned a01 = __byte_perm(X0, X1, 0x6240), a23 = __byte_perm(X2, X3, 0x6240);   // {b0,b0',b2,b2'}
+      const unsigned w0 = __byte_perm(a01, a23, 0x5410), w2 = __byte_perm(a01, a23, 0x7632);
+      const unsigned w1 = __byte_perm(__byte_perm(X0, X1, 0x0051), __byte_perm(X2, X3, 0x0051), 0x5410);
+      tmp[k] = w0; tmp[8 + k] = w1; tmp[16 + k] = w2;
+      const int hh = BL == 1 ? 0 : half;
+      sl[0][hh] = dp4a_uu(w0, 0x01010101u, sl[0][hh]);
+      sl[1][hh] = dp4a_uu(w1, 0x01010101u, sl[1][hh]);
+      sl[2][hh] = dp4a_su(w2, 0x01010101u, sl[2][hh]);
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < 24; t++) x.xw[t] = tmp[t];
+  const int sx0 = sl[0][0] + (sl[1][0] << 8) + (sl[2][0] << 16), sx1 = sl[0][1] + (sl[1][1] << 8) + (sl[2][1] << 16);
+  x.mt = make_float4(sf, sf * (float)(sx0 + sx1), sf * (float)sx0, sf * (float)sx1);
+#pragma unroll
+  for (int i = 0; i < 6; i++) x.iv[i] = 0;
+  if constexpr (QCfg<F>::INT_MID) {
+    if constexpr (QCfg<F>::HALVES) {
+#pragma unroll
+      for (int l = 0; l < 3; l++) { x.iv[l * 2] = -fi.mid * sl[l][0]; x.iv[l * 2 + 1] = -fi.mid * sl[l][1]; }
+    } else {
+#pragma unroll
+      for (int l = 0; l < 3; l++) x.iv[l * 2] = -fi.mid * (sl[l][0] + sl[l][1]);
+    }
+  }
+}
+
+// Contribution of one chunk-row (32 weights of one output row) to that row's sum.
+template <int F>
+__device__ __forceinline__ float idot_chunk(const FragT<F>& f, const XQRegs& x) {
+  constexpr WvFmtInfo fi = wv_fmt_info(F);
+  constexpr int BL = fi.bits_lo, BH = fi.bits_hi, SPW = 8 / BL;
+  constexpr unsigned MASK = 0x01010101u * ((1u << BL) - 1u);
+  constexpr unsigned MASKH = BH ? (0x01010101u * ((1u << BH) - 1u)) << BL : 0u;
+  constexpr bool HALVES = QCfg<F>::HALVES;
+  constexpr int NH = QCfg<F>::NH;
+  // accumulators [limb][half][parity]: two independent chains per sum keep the dp4a pipe fed
+  int I[3][2][2];
+#pragma unroll
+  for (int l = 0; l < 3; l++) { I[l][0][0] = x.iv[l * 2]; I[l][1][0] = HALVES ? x.iv[l * 2 + 1] : 0; I[l][0][1] = 0; I[l][1][1] = 0; }
+#pragma unroll
+  for (int k = 0; k < 8; k++) {
+    const int w = k / SPW, sh = k % SPW;
+    unsigned bytes = (f.lo[w] >> (BL * sh)) & MASK;
+    if constexpr (BH > 0) {
+      const int hw = (k * BH) >> 3, hs = (k * BH) & 7;
+      unsigned hv = f.hi[hw];
+      hv = hs >= BL ? (hv >> (hs - BL)) : (hv << (BL - hs));
+      bytes |= hv & MASKH;
+    }
+    const int h = (HALVES && k >= 4) ? 1 : 0;  // first / second 16 weights of the chunk
+    const int p = k & 1;
+    I[0][h][p] = dp4a_uu(bytes, x.xw[k], I[0][h][p]);
+    I[1][h][p] = dp4a_uu(bytes, x.xw[8 + k], I[1][h][p]);
+    I[2][h][p] = dp4a_us(bytes, x.xw[16 + k], I[2][h][p]);
+  }
+  float val[2];
+#pragma unroll
+  for (int h = 0; h < NH; h++) {
+    const int i0 = I[0][h][0] + I[0][h][1], i1 = I[1][h][0] + I[1][h][1], i2 = I[2][h][0] + I[2][h][1];
+    val[h] = fmaf(65536.0f, (float)i2, (float)(i0 + (i1 << 8)));
+  }
+  const float4 mt = x.mt;
+  float v, extra = 0.f;
+  if constexpr (fi.kind == WK_KQUANT) {
+    // scale bytes were remapped 0 -> 1 at upload (kquant.go:180-182: a zero group scale
+    // decodes as d/255), so no test is needed here
+    const float t = u8f(f.pr[2], 0) * val[0] + u8f(f.pr[2], 1) * val[1];
+    v = (__uint_as_float(f.pr[0]) * (1.0f / 255.0f)) * t;
+    if constexpr (fi.has_min) {
+      const unsigned mb = f.pr[2] ^ 0x80800000u;  // int8 -> biased uint8
+      const float mm = (__uint_as_float(__byte_perm(mb, 0x4B000000u, 0x7652)) - 8388736.0f) * mt.z +
+                       (__uint_as_float(__byte_perm(mb, 0x4B000000u, 0x7653)) - 8388736.0f) * mt.w;
+      extra = (__uint_as_float(f.pr[1]) * (1.0f / 127.0f)) * mm;
+    }
+  } else if constexpr (fi.kind == WK_CLASSIC || fi.kind == WK_AFFINE) {
+    v = __uint_as_float(f.pr[0]) * val[0];
+    if constexpr (fi.has_min) extra = __uint_as_float(f.pr[1]) * mt.y;
+  } else if constexpr (fi.kind == WK_TERNARY) {
+    v = __uint_as_float(f.pr[0]) * val[0] + __uint_as_float(f.pr[1]) * val[1];
+  } else if constexpr (fi.sign) {
+    v = __uint_as_float(f.pr[0]) * (2.0f * val[0]);
+    extra = -__uint_as_float(f.pr[0]) * mt.y;
+  } else {  // IQ linear grids: (code - mid - 0.5)
+    constexpr float hm = (float)fi.mid + 0.5f;
+    if constexpr (HALVES) {
+      v = __uint_as_float(f.pr[0]) * val[0] + __uint_as_float(f.pr[1]) * val[1];
+      extra = -hm * (__uint_as_float(f.pr[0]) * mt.z + __uint_as_float(f.pr[1]) * mt.w);
+    } else {
+      v = __uint_as_float(f.pr[0]) * val[0];
+      extra = -hm * __uint_as_float(f.pr[0]) * mt.y;
+    }
+  }
+  return fmaf(mt.x, v, extra);
+}
+
+// Launch with programmatic dependent launch allowed: the kernel may start while its
+// predecessor drains and must execute griddepcontrol.wait before touching dependent data.
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
+// wv_gemv.cu
+uint4* wv_scratch_take(size_t bytes);
+int wv_launch_xquant(int bits_lo, const float* dx, int cols, int batch, int imid, uint4* out, cudaStream_t st);
+int wv_sm_count();
+// wv_gemv_tma.cu: returns WV_OK, an error, or 1 when the shape does not fit the TMA kernel
+int wv_launch_gemv_tma(const WvDevBlob& b, const float* dx, float* dy, int batch, int row_begin, int row_end, cudaStream_t st);

@@ -1,0 +1,477 @@
+// TMA-fed GEMV for sm_100a: the packed planes of a band of rows are pulled into a shared-memory
+// ring by bulk asynchronous copies (cp.async.bulk + mbarrier), so the bytes in flight per SM
+// are set by the ring depth (100-200 KB) rather than by registers, and the consumer warps never
+// compute a global address.
+//
+//   * one CTA per SM owns a contiguous band of output rows; a producer thread streams the band
+//     tile by tile (TR rows of every plane, each plane's rows contiguous -> one bulk copy per
+//     plane per tile) through STAGES buffers guarded by full/empty mbarriers;
+//   * weights do not depend on the preceding kernel, so the producer starts before
+//     griddepcontrol.wait (programmatic dependent launch overlaps the previous kernel's tail);
+//   * every consumer lane owns one 32-column chunk for the whole kernel and keeps that chunk's
+//     quantised activations in registers (no per-step activation loads); a row's partial sums
+//     are reduced with warp shuffles and then across the column warps through shared memory,
+//     32 rows at a time, so y is written with coalesced stores;
+//   * all waits on mbarriers are bounded: when a wait runs out the CTA records an error code,
+//     stops issuing copies, drains the ones in flight (bounded again) and returns.
+#include "wv_gemv_common.cuh"
+
+#define TMA_CONSUMER_WARPS 16
+#define TMA_THREADS ((TMA_CONSUMER_WARPS + 1) * 32)
+#define TMA_MAX_STAGES 8
+#define TMA_SPIN_LIMIT (1u << 22)
+
+struct TmaGeom {
+  int cpr;           // chunks per row
+  int nwc;           // column warps per row (ceil(cpr/32))
+  int nrg;           // row groups working side by side on one tile
+  int tr;            // rows per tile = nrg * RT
+  int nstage;
+  unsigned stage_bytes;
+  unsigned off[5];   // lo, hi, p0, p1, km section offsets inside a stage
+  unsigned rb[5];    // bytes per row of each plane (0 = plane absent)
+  unsigned x_off;    // staged activations: 33 floats per chunk (32 + one of padding)
+  unsigned red_off;  // float red[2][nrg][nwc][32]
+  unsigned bar_off;  // full[nstage], empty[nstage]
+};
+
+// Sticky code of the first bounded wait that ran out, in mapped pinned host memory so that the
+// host can poll it without a CUDA call.
+static int* g_err_host = nullptr;
+static int* g_err_dev = nullptr;
+#ifdef WV_PHASES  // development aid: per-CTA clock stamps (start, x ready, first tile ready, end)
+static __device__ long long* g_dbg = nullptr;
+extern "C" void wv_debug_set_buffer(long long* p) { cudaMemcpyToSymbol(g_dbg, &p, sizeof p); }
+#define WV_STAMP(i) do { if (g_dbg && threadIdx.x == 0) g_dbg[blockIdx.x * 8 + (i)] = clock64(); } while (0)
+#else
+#define WV_STAMP(i) do {} while (0)
+#endif
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait: returns false when the phase did not complete within the spin limit.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
+  for (unsigned i = 0; i < TMA_SPIN_LIMIT; i++) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ unsigned lds32(unsigned a) { unsigned v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+__device__ __forceinline__ unsigned lds16(unsigned a) { unsigned short v; asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a)); return v; }
+__device__ __forceinline__ uint2 lds64(unsigned a) { uint2 v; asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a)); return v; }
+__device__ __forceinline__ uint4 lds128(unsigned a) { uint4 v; asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a)); return v; }
+
+// Per-lane shared-memory addresses (32-bit) of this lane's chunk in row 0 of its row group,
+// relative to a stage base; a row further down adds the plane's row bytes.
+struct LaneOff { unsigned lo, hi, p0, p1, km; };
+
+template <int F>
+__device__ __forceinline__ LaneOff lane_offsets(const TmaGeom& g, int row0, int c, int group) {
+  constexpr WvFmtInfo fi = wv_fmt_info(F);
+  LaneOff o;
+  o.lo = g.off[0] + row0 * g.rb[0] + c * fi.bits_lo * 4;
+  o.hi = g.off[1] + row0 * g.rb[1] + c * fi.bits_hi * 4;
+  unsigned pi;
+  if constexpr (fi.kind == WK_KQUANT) pi = (c >> 3) * 8;
+  else if constexpr (fi.kind == WK_BINARY || fi.kind == WK_AFFINE) pi = ((c * 32) / group) * 4;
+  else if constexpr (fi.pgroup == 16) pi = c * 8;
+  else pi = c * 4;
+  o.p0 = g.off[2] + row0 * g.rb[2] + pi;
+  o.p1 = g.off[3] + row0 * g.rb[3] + pi;
+  o.km = g.off[4] + row0 * g.rb[4] + c * (fi.has_min ? 4 : 2);
+  return o;
+}
+
+// Weight fragment at addresses a.* (already advanced to the wanted row and stage).
+template <int F>
+__device__ __forceinline__ void load_frag_smem(FragT<F>& f, const LaneOff& a) {
+  constexpr WvFmtInfo fi = wv_fmt_info(F);
+  constexpr int BL = fi.bits_lo, BH = fi.bits_hi;
+  if constexpr (BL == 1) f.lo[0] = lds32(a.lo);
+  else if constexpr (BL == 2) { const uint2 v = lds64(a.lo); f.lo[0] = v.x; f.lo[1] = v.y; }
+  else if constexpr (BL == 4) { const uint4 v = lds128(a.lo); f.lo[0] = v.x; f.lo[1] = v.y; f.lo[2] = v.z; f.lo[3] = v.w; }
+  else {
+    const uint4 v = lds128(a.lo), u = lds128(a.lo + 16);
+    f.lo[0] = v.x; f.lo[1] = v.y; f.lo[2] = v.z; f.lo[3] = v.w; f.lo[4] = u.x; f.lo[5] = u.y; f.lo[6] = u.z; f.lo[7] = u.w;
+  }
+  if constexpr (BH == 1) f.hi[0] = lds32(a.hi);
+  if constexpr (BH == 2) { const uint2 v = lds64(a.hi); f.hi[0] = v.x; f.hi[1] = v.y; }
+  if constexpr (fi.kind == WK_KQUANT) {
+    const uint2 dd = lds64(a.p0);
+    f.pr[0] = dd.x; f.pr[1] = dd.y;
+    if constexpr (fi.has_min) f.pr[2] = lds32(a.km); else f.pr[2] = lds16(a.km);
+  } else if constexpr (fi.kind == WK_CLASSIC || fi.kind == WK_AFFINE) {
+    f.pr[0] = lds32(a.p0);
+    if constexpr (fi.has_min) f.pr[1] = lds32(a.p1);
+  } else if constexpr (fi.pgroup == 16) {
+    const uint2 v = lds64(a.p0);
+    f.pr[0] = v.x; f.pr[1] = v.y;
+  } else {
+    f.pr[0] = lds32(a.p0);
+  }
+}
+
+template <int F, int RT>
+__global__ void __launch_bounds__(TMA_THREADS, 1)
+gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* __restrict__ xf, float* __restrict__ y,
+                int row_begin, int row_end, const TmaGeom g, int* __restrict__ err) {
+  constexpr WvFmtInfo fi = wv_fmt_info(F);
+  constexpr int BL = fi.bits_lo;
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ int s_abort;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nrows = row_end - row_begin;
+  const int c_lo = (int)(((long long)blockIdx.x * nrows) / gridDim.x), c_hi = (int)(((long long)(blockIdx.x + 1) * nrows) / gridDim.x);
+  const int band = c_hi - c_lo;
+  const int ntiles = (band + g.tr - 1) / g.tr;
+  const unsigned bar0 = smem_u32(smem + g.bar_off);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (g.nstage + s); };
+  const int nactive = g.nrg * g.nwc;  // consumer warps that take part
+
+  if (tid == 0) {
+    s_abort = 0;
+    for (int s = 0; s < g.nstage; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), nactive); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if constexpr (fi.table) {
+    float* tbl = reinterpret_cast<float*>(smem + g.red_off) + 2 * g.nrg * g.nwc * 32;
+    for (int i = tid; i < 512; i += TMA_THREADS) tbl[i] = c_grid4nl[i >> 5];
+  }
+  __syncthreads();
+
+  if (warp == TMA_CONSUMER_WARPS) {
+    // ------------------------------------------------------------ producer
+    // One thread issues the copies. The whole warp stays convergent around the named barrier
+    // (bar.sync counts whole warps), so the loop is split at the barrier instead of calling
+    // it from inside the single-thread branch.
+    const void* src[5] = {b.lo, b.hi, b.p0, b.p1, b.km};
+    bool dead = false;
+    int issued = 0;
+    auto issue_tile = [&](int t) {
+      const int s = t % g.nstage;
+      if (t >= g.nstage) {
+        if (*(volatile int*)&s_abort || !mbar_wait(empty_bar(s), ((t / g.nstage) - 1) & 1)) {
+          if (!*(volatile int*)&s_abort) { atomicCAS_system(err, 0, 100 + s); *(volatile int*)&s_abort = 1; }
+          dead = true;
+          return;
+        }
+      }
+      const int r0 = c_lo + t * g.tr;
+      const int nr = min(g.tr, c_hi - r0);
+      unsigned bytes = 0;
+#pragma unroll
+      for (int i = 0; i < 5; i++) bytes += g.rb[i] * nr;
+      mbar_expect_tx(full_bar(s), bytes);
+      const unsigned dst = smem_u32(smem) + (unsigned)s * g.stage_bytes;
+#pragma unroll
+      for (int i = 0; i < 5; i++) {
+        if (g.rb[i]) bulk_g2s(dst + g.off[i], (const unsigned char*)src[i] + (size_t)(row_begin + r0) * g.rb[i], g.rb[i] * nr, full_bar(s));
+      }
+      issued = t + 1;
+    };
+    if (lane == 0 && ntiles > 0) issue_tile(0);
+    __syncwarp();
+    // The activation loads must not queue behind a full ring of weight traffic: after the
+    // first tile, hold further copies until every consumer has issued its loads of x.
+    asm volatile("bar.sync 14, %0;" ::"n"(TMA_CONSUMER_WARPS * 32 + 32) : "memory");
+    if (lane == 0) {
+      for (int t = 1; t < ntiles && !dead; t++) issue_tile(t);
+      // drain: every copy issued must have landed before the CTA gives its shared memory back
+      for (int t = max(0, issued - g.nstage); t < issued; t++) {
+        if (!mbar_wait(full_bar(t % g.nstage), (t / g.nstage) & 1)) { atomicCAS_system(err, 0, 200 + t % g.nstage); break; }
+      }
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------- consumers
+  const int wc = warp % g.nwc, rg = warp / g.nwc;
+  const int c = wc * 32 + lane;
+  const bool live = c < g.cpr;
+
+  WV_STAMP(0);
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  WV_STAMP(1);
+  // All consumer warps copy x into shared memory with coalesced loads; each chunk of 32
+  // floats gets a 33-float slot so that lanes reading their own chunks element by element
+  // hit 32 different banks.
+  {
+    const float* xrow = xf + (size_t)blockIdx.y * b.cols;
+    float* xs = reinterpret_cast<float*>(smem + g.x_off);
+    const int nv = b.cols >> 2;
+    if ((reinterpret_cast<uintptr_t>(xrow) & 15) == 0) {
+      // cols <= 16384: at most 8 vectors per thread; all loads are issued before the first
+      // store so that the copy costs one memory round trip, not eight
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const int i = tid + u * TMA_CONSUMER_WARPS * 32;
+        if (i < nv) v[u] = __ldg(reinterpret_cast<const float4*>(xrow) + i);
+      }
+      asm volatile("bar.arrive 14, %0;" ::"n"(TMA_CONSUMER_WARPS * 32 + 32) : "memory");
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const int i = tid + u * TMA_CONSUMER_WARPS * 32;
+        if (i < nv) { float* d = xs + (i >> 3) * 33 + (i & 7) * 4; d[0] = v[u].x; d[1] = v[u].y; d[2] = v[u].z; d[3] = v[u].w; }
+      }
+    } else {
+      asm volatile("bar.arrive 14, %0;" ::"n"(TMA_CONSUMER_WARPS * 32 + 32) : "memory");
+      for (int i = tid; i < b.cols; i += TMA_CONSUMER_WARPS * 32) xs[(i >> 5) * 33 + (i & 31)] = __ldg(xrow + i);
+    }
+  }
+  asm volatile("bar.sync 15, %0;" ::"n"(TMA_CONSUMER_WARPS * 32) : "memory");
+  if (rg >= g.nrg) return;
+  XQRegs xr;
+  float4 xfr[8];
+  const float* tbl = nullptr;
+  {
+    const float* xc = reinterpret_cast<const float*>(smem + g.x_off) + (size_t)c * 33;
+    if constexpr (fi.table) {
+      tbl = reinterpret_cast<const float*>(smem + g.red_off) + 2 * g.nrg * g.nwc * 32 + lane;
+      if (live) {
+        const float* xp = xc;
+#pragma unroll
+        for (int k = 0; k < 8; k++)
+          xfr[k] = make_float4(xp[WvLane<BL>::j_of(k, 0)], xp[WvLane<BL>::j_of(k, 1)], xp[WvLane<BL>::j_of(k, 2)], xp[WvLane<BL>::j_of(k, 3)]);
+      }
+    } else {
+      if (live) quantize_chunk<F>(xr, xc);
+    }
+  }
+  WV_STAMP(2);
+  float* red = reinterpret_cast<float*>(smem + g.red_off);
+  float* yb = y + (size_t)blockIdx.y * b.rows + row_begin;
+  float keep = 0.f;
+  int par = 0;
+  bool dead = false;
+  const int nslots = ntiles * RT;
+  auto flush = [&](int batch_base) {
+    float* mine = red + (((size_t)par * g.nrg + rg) * g.nwc + wc) * 32;
+    mine[lane] = keep;
+    asm volatile("bar.sync %0, %1;" ::"r"(rg + 1), "r"(g.nwc * 32) : "memory");
+    if (wc == 0) {
+      const float* base = red + ((size_t)par * g.nrg + rg) * g.nwc * 32;
+      float sum = 0.f;
+      for (int q = 0; q < g.nwc; q++) sum += base[q * 32 + lane];
+      const int n = batch_base + lane;
+      const int row = c_lo + (n / RT) * g.tr + rg * RT + (n % RT);
+      if (n < nslots && (n / RT) * g.tr + rg * RT + (n % RT) < band && rg * RT + (n % RT) < g.tr) yb[row] = sum;
+    }
+    par ^= 1;
+    keep = 0.f;
+  };
+
+  const unsigned sbase = smem_u32(smem);
+  const LaneOff lo0 = lane_offsets<F>(g, rg * RT, live ? c : 0, b.group);
+  // Fetch the fragments of tile t from the ring into registers, then hand the stage back.
+  auto wait_tile = [&](int t, bool block) -> bool {
+    const int s = t % g.nstage;
+    if (dead || *(volatile int*)&s_abort) { dead = true; return true; }
+    if (!block) {
+      unsigned ok;
+      asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                   : "=r"(ok) : "r"(full_bar(s)), "r"((unsigned)((t / g.nstage) & 1)) : "memory");
+      return __all_sync(0xffffffffu, ok != 0);
+    }
+    if (!mbar_wait(full_bar(s), (t / g.nstage) & 1)) {
+      atomicCAS_system(err, 0, 300 + s); *(volatile int*)&s_abort = 1; dead = true;
+    }
+    return true;
+  };
+  auto fetch_tile = [&](FragT<F> (&fr)[RT], int t) {
+    const int s = t % g.nstage;
+    const int nr = min(g.tr, band - t * g.tr);
+    LaneOff a = lo0;
+    const unsigned st = sbase + (unsigned)s * g.stage_bytes;
+    a.lo += st; a.hi += st; a.p0 += st; a.p1 += st; a.km += st;
+#pragma unroll
+    for (int rr = 0; rr < RT; rr++) {
+      if (live && !dead && rg * RT + rr < nr) load_frag_smem<F>(fr[rr], a);
+      a.lo += g.rb[0]; a.hi += g.rb[1]; a.p0 += g.rb[2]; a.p1 += g.rb[3]; a.km += g.rb[4];
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty_bar(s));  // the fragments are in registers: hand the stage back
+  };
+
+  FragT<F> nxt[RT];
+  if (ntiles > 0) { wait_tile(0, true); fetch_tile(nxt, 0); }
+  WV_STAMP(3);
+  for (int t = 0; t < ntiles; t++) {
+    const int nr = min(g.tr, band - t * g.tr);
+    FragT<F> fr[RT];
+#pragma unroll
+    for (int rr = 0; rr < RT; rr++) fr[rr] = nxt[rr];
+    // prefetch the next tile's fragments before computing when they have already landed
+    bool fetched = true;
+    if (t + 1 < ntiles) {
+      fetched = wait_tile(t + 1, false);
+      if (fetched) fetch_tile(nxt, t + 1);
+    }
+    float v[RT];
+#pragma unroll
+    for (int rr = 0; rr < RT; rr++) {
+      const int lr = rg * RT + rr;
+      v[rr] = 0.f;
+      if (live && !dead && lr < nr) {
+        if constexpr (fi.table) v[rr] = chunk_value<F>(fr[rr], xfr, make_float2(0.f, 0.f), tbl);
+        else v[rr] = idot_chunk<F>(fr[rr], xr);
+      }
+    }
+    // Transposing reduction: RT row sums per lane -> every lane ends with the warp total of one
+    // row; the lane whose index equals the row's slot (n & 31) keeps it.
+    float tot;
+    if constexpr (RT == 4) {
+      const bool b4 = lane & 16, b3 = lane & 8;
+      float a0 = b4 ? v[2] : v[0], a1 = b4 ? v[3] : v[1];
+      a0 += __shfl_xor_sync(0xffffffffu, b4 ? v[0] : v[2], 16);
+      a1 += __shfl_xor_sync(0xffffffffu, b4 ? v[1] : v[3], 16);
+      tot = b3 ? a1 : a0;
+      tot += __shfl_xor_sync(0xffffffffu, b3 ? a0 : a1, 8);
+#pragma unroll
+      for (int o = 4; o; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+      tot = __shfl_sync(0xffffffffu, tot, (lane & 3) * 8);  // row (lane & 3) lives in lanes [8*(lane&3), +8)
+      if ((lane >> 2) == (t & 7)) keep = tot;
+    } else if constexpr (RT == 2) {
+      const bool b4 = lane & 16;
+      tot = b4 ? v[1] : v[0];
+      tot += __shfl_xor_sync(0xffffffffu, b4 ? v[0] : v[1], 16);
+#pragma unroll
+      for (int o = 8; o; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+      tot = __shfl_sync(0xffffffffu, tot, (lane & 1) * 16);
+      if ((lane >> 1) == (t & 15)) keep = tot;
+    } else {
+      tot = v[0];
+#pragma unroll
+      for (int o = 16; o; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+      if (lane == (t & 31)) keep = tot;
+    }
+    if (((t * RT + RT - 1) & 31) == 31) flush(t * RT + RT - 32);
+    if (!fetched) { wait_tile(t + 1, true); fetch_tile(nxt, t + 1); }
+  }
+  if (nslots & 31) flush(nslots & ~31);
+  WV_STAMP(4);
+}
+
+// ------------------------------------------------------------------ host side
+static unsigned align128(unsigned v) { return (v + 127u) & ~127u; }
+
+// Bytes per row of each plane in the device layout; false when a plane's rows are not
+// 16-byte multiples (then consecutive rows cannot be fetched by bulk copies).
+static bool plane_row_bytes(const WvDevBlob& b, unsigned rb[5]) {
+  const WvFmtInfo fi = wv_fmt_info(b.format);
+  const unsigned cpr = (unsigned)(b.cols >> 5);
+  rb[0] = cpr * fi.bits_lo * 4; rb[1] = cpr * fi.bits_hi * 4; rb[2] = rb[3] = rb[4] = 0;
+  switch (fi.kind) {
+  case WK_CLASSIC: rb[2] = cpr * 4; rb[3] = fi.has_min ? cpr * 4 : 0; break;
+  case WK_KQUANT: if (cpr % 8) return false; rb[2] = cpr; rb[4] = cpr * (fi.has_min ? 4 : 2); break;
+  case WK_IQ: case WK_TERNARY: rb[2] = cpr * (fi.pgroup == 16 ? 8 : 4); break;
+  case WK_BINARY: if ((b.cols % b.group) || (b.group % 32)) return false; rb[2] = (unsigned)(b.cols / b.group) * 4; break;
+  case WK_AFFINE: if ((b.cols % b.group) || (b.group % 32)) return false; rb[2] = rb[3] = (unsigned)(b.cols / b.group) * 4; break;
+  default: return false;
+  }
+  for (int i = 0; i < 5; i++) if (rb[i] % 16) return false;
+  return true;
+}
+
+static int g_tma_rt = 0, g_tma_stages = 0;
+extern "C" void wv_set_tma_tuning(int rows_per_group, int stages) { g_tma_rt = rows_per_group; g_tma_stages = stages; }
+
+template <int F, int RT>
+static int launch_tma(const WvDevBlob& b, const float* dx, float* dy, int batch, int rb_, int re, cudaStream_t st) {
+  constexpr WvFmtInfo fi = wv_fmt_info(F);
+  TmaGeom g{};
+  if (!plane_row_bytes(b, g.rb)) return 1;
+  g.cpr = b.cols >> 5;
+  g.nwc = (g.cpr + 31) / 32;
+  if (g.nwc > TMA_CONSUMER_WARPS) return 1;
+  g.nrg = TMA_CONSUMER_WARPS / g.nwc;
+  if (g.nrg > 8) g.nrg = 8;
+  g.tr = g.nrg * RT;
+  unsigned off = 0;
+  for (int i = 0; i < 5; i++) { g.off[i] = off; off = align128(off + g.rb[i] * g.tr); }
+  g.stage_bytes = off;
+  const unsigned xbytes = align128((unsigned)g.cpr * 132u);
+  const unsigned fixed = xbytes + align128(2u * g.nrg * g.nwc * 32 * 4 + (fi.table ? 2048u : 0u)) + 2 * TMA_MAX_STAGES * 8 + 128;
+  const unsigned avail = 225u * 1024u;  // 227 KB per CTA minus static shared memory and slack
+  if (g.stage_bytes * 2 + fixed > avail) return 1;
+  int ns = (int)((avail - fixed) / g.stage_bytes);
+  if (ns > TMA_MAX_STAGES) ns = TMA_MAX_STAGES;
+  if (g_tma_stages > 1 && g_tma_stages < ns) ns = g_tma_stages;
+  g.nstage = ns;
+  g.x_off = g.stage_bytes * ns;
+  g.red_off = g.x_off + xbytes;
+  g.bar_off = align128(g.red_off + 2u * g.nrg * g.nwc * 32 * 4 + (fi.table ? 2048u : 0u));
+  const size_t smem = g.bar_off + 2 * TMA_MAX_STAGES * 8;
+
+  auto kern = gemv_tma_kernel<F, RT>;
+  static unsigned attr_mask = 0;
+  int dev = 0; cudaGetDevice(&dev);
+  if (!(attr_mask & (1u << dev))) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) != cudaSuccess) { wv_set_error("gemv (tma): cannot raise the shared-memory limit"); return WV_ECUDA; }
+    attr_mask |= 1u << dev;
+  }
+  int grid = wv_sm_count();
+  const int nrows = re - rb_;
+  if (grid > nrows) grid = nrows;
+  const uint4* xq = nullptr;  // activations are quantised inside the kernel
+  cudaError_t e = launch_pdl(kern, dim3(grid, batch), dim3(TMA_THREADS), smem, st, b, xq, dx, dy, rb_, re, g, g_err_dev);
+  if (e != cudaSuccess) { wv_set_error("gemv (tma) launch: %s", cudaGetErrorString(e)); return WV_ECUDA; }
+  return WV_OK;
+}
+
+template <int F>
+static int launch_tma_format(const WvDevBlob& b, const float* dx, float* dy, int batch, int rb, int re, cudaStream_t st) {
+  constexpr WvFmtInfo fi = wv_fmt_info(F);
+  int rt = g_tma_rt ? g_tma_rt : (fi.bits_lo == 8 ? 2 : 4);
+  if (rt == 1) return launch_tma<F, 1>(b, dx, dy, batch, rb, re, st);
+  if (rt == 2) return launch_tma<F, 2>(b, dx, dy, batch, rb, re, st);
+  return launch_tma<F, 4>(b, dx, dy, batch, rb, re, st);
+}
+
+int wv_launch_gemv_tma(const WvDevBlob& b, const float* dx, float* dy, int batch, int row_begin, int row_end, cudaStream_t st) {
+  switch (b.format) {
+#define WV_F(f) case f: return launch_tma_format<f>(b, dx, dy, batch, row_begin, row_end, st);
+  WV_F(WV_Q8_0) WV_F(WV_Q4_0) WV_F(WV_Q4_1) WV_F(WV_Q5_0) WV_F(WV_Q5_1)
+  WV_F(WV_Q2_K) WV_F(WV_Q3_K) WV_F(WV_Q4_K) WV_F(WV_Q5_K) WV_F(WV_Q6_K)
+  WV_F(WV_IQ1_S) WV_F(WV_IQ2_XXS) WV_F(WV_IQ2_XS) WV_F(WV_IQ3_XXS) WV_F(WV_IQ3_S) WV_F(WV_IQ4_NL) WV_F(WV_IQ4_XS)
+  WV_F(WV_TERNARY) WV_F(WV_BINARY) WV_F(WV_AFFINE)
+#undef WV_F
+  }
+  return 1;
+}
+
+// Code of the first bounded device wait that ran out (0 = none); reading clears it.
+int wv_tma_take_error() {
+  if (!g_err_host) return 0;
+  const int v = *(volatile int*)g_err_host;
+  if (v) *(volatile int*)g_err_host = 0;
+  return v;
+}
+int wv_tma_init() {
+  if (g_err_host) return WV_OK;
+  if (cudaHostAlloc(&g_err_host, sizeof(int), cudaHostAllocMapped) != cudaSuccess) { cudaGetLastError(); return WV_ENOMEM; }
+  *g_err_host = 0;
+  if (cudaHostGetDevicePointer(&g_err_dev, g_err_host, 0) != cudaSuccess) { cudaGetLastError(); return WV_ECUDA; }
+  return WV_OK;
+}
