@@ -1,0 +1,130 @@
+"""CPU tests of the boundary and the host-side mirror: the shared library loads and exports
+every symbol the header declares, status codes without a device, size formulas against the
+oracle, shard ranges, the wire codec of the host mirror, and a two-rank gloo run of the
+row-shard bookkeeping."""
+import ctypes as C
+import os
+import re
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import oracle as O
+from conftest import CASES, case_id, case_ok, make_w, ROOT
+
+
+def _lib():
+    from welvet_b200 import _lib
+    return _lib
+
+
+def test_library_exports_every_declared_symbol():
+    L = _lib().lib()
+    header = open(os.path.join(ROOT, "include", "welvet_cuda.h")).read()
+    declared = set(re.findall(r"\b(wv_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    assert declared == set(_lib().SYMBOLS), declared ^ set(_lib().SYMBOLS)
+    for s in declared:
+        assert hasattr(L, s), s
+
+
+def test_status_codes_without_a_device():
+    m = _lib()
+    L = m.lib()
+    if L.wv_device_count() > 0:
+        pytest.skip("a device is present")
+    assert L.wv_available() == 0
+    assert L.wv_init(0) == m.WV_EINIT and b"no CUDA device" in L.wv_last_error()
+    x = np.zeros(8, np.float32)
+    assert L.wv_matvec(1, x.ctypes.data, x.ctypes.data, 1, 8, 8) == m.WV_EINIT  # no CPU fallback
+    assert L.wv_blob_has(1) == 0 and L.wv_cache_bytes() == 0
+
+
+@pytest.mark.parametrize("case", CASES, ids=case_id)
+def test_pack_sizes_match_oracle(case):
+    f, bw, dt = case
+    L = _lib().lib()
+    for rows, cols in ((8, 256), (3, 100), (5, 4096), (1, 31)):
+        if not case_ok(case, rows, cols):
+            continue
+        a, b, c = C.c_size_t(), C.c_size_t(), C.c_size_t()
+        assert L.wv_pack_sizes(O.FMT[f], dt, bw, rows, cols, C.byref(a), C.byref(b), C.byref(c)) == 0
+        assert (a.value, b.value, c.value) == O.sizes(f, rows, cols, bw, dt)
+
+
+def test_pack_sizes_errors_and_shard_range():
+    m = _lib()
+    L = m.lib()
+    a = C.c_size_t()
+    assert L.wv_pack_sizes(2, 1, 0, 0, 5, C.byref(a), None, None) == m.WV_ESHAPE
+    assert L.wv_pack_sizes(99, 1, 0, 4, 32, C.byref(a), None, None) == m.WV_EFORMAT
+    assert L.wv_pack_sizes(0, 7, 0, 4, 32, C.byref(a), None, None) == m.WV_EFORMAT
+    assert L.wv_pack_sizes(20, 1, 64, 4, 96, C.byref(a), None, None) == m.WV_ESHAPE   # affine cols % group
+    assert L.wv_pack_sizes(19, 1, 128, 4, 96, C.byref(a), None, None) == m.WV_ESHAPE  # g128 cols % 128
+    lo, hi = C.c_int(), C.c_int()
+    covered = []
+    for r in range(8):
+        assert L.wv_shard_range(128256, r, 8, C.byref(lo), C.byref(hi)) == 0
+        covered.append((lo.value, hi.value))
+    assert covered[0][0] == 0 and covered[-1][1] == 128256
+    assert all(covered[i][1] == covered[i + 1][0] for i in range(7)) and all(h - l == 16032 for l, h in covered)
+    assert L.wv_shard_range(10, 3, 3, C.byref(lo), C.byref(hi)) == m.WV_EARG
+
+
+def test_host_mirror_wire_codec_matches_oracle():
+    from welvet_b200 import quant, weights
+    rows, cols = 6, 256
+    w, _ = make_w(2, rows, cols)
+    for f, bw in (("Q4_K", 0), ("IQ3_S", 0), ("BinaryPacked", 128), ("AffinePacked", 64), ("TernaryPacked", 0)):
+        ob = O.pack(f, w, rows, cols, bw)
+        pb = quant.Blob(quant.Format(ob.format), rows, cols, ob.raw, ob.scales, ob.mins, ob.block_weights)
+        wire = weights.EncodePackedWire(pb)
+        assert wire == O.wire_encode(ob).tobytes()
+        back = weights.DecodePackedWire(pb.Format, rows, cols, wire)
+        assert np.array_equal(back.Raw, ob.raw) and np.array_equal(back.Scales, ob.scales) and np.array_equal(back.Mins, ob.mins)
+        if f == "BinaryPacked":
+            assert back.BlockWeights == 128
+    with pytest.raises(Exception):
+        weights.DecodePackedWire(quant.Format.FormatQ4_K, rows, cols, wire[:20])
+    assert quant.ParseFormatName("Q4_K") == quant.Format.FormatQ4_K and quant.Format.FormatIQ2_XXS.String() == "IQ2_XXS"
+    assert quant.ParseFormatName("") == quant.Format.FormatNone and quant.Format.FormatQ6_K.IsKQuant()
+
+
+WORKER = r'''
+import os, sys, ctypes as C
+import numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["WV_ROOT"])
+import oracle as O
+from welvet_b200 import _lib
+dist.init_process_group("gloo")
+rank, world = dist.get_rank(), dist.get_world_size()
+L = _lib.lib()
+rows, cols = 64, 512
+w = np.random.default_rng(11).normal(0, 0.02, (rows, cols)).astype(np.float32)
+x = np.random.default_rng(12).normal(0, 1, cols).astype(np.float32)
+lo, hi = C.c_int(), C.c_int()
+assert L.wv_shard_range(rows, rank, world, C.byref(lo), C.byref(hi)) == 0
+# each rank computes its slice with the oracle standing in for the device, then all-gathers
+ob = O.pack("Q4_K", w[lo.value:hi.value], hi.value - lo.value, cols)
+part = torch.from_numpy(O.matvec_simd(ob, x, 1))
+full = torch.zeros(rows)
+dist.all_gather_into_tensor(full, part)
+ref = O.matvec_simd(O.pack("Q4_K", w, rows, cols), x, 1)
+assert np.array_equal(full.numpy(), ref), "row shards do not reassemble"
+dist.barrier()
+dist.destroy_process_group()
+'''
+
+
+def test_row_shard_bookkeeping_two_ranks_gloo(tmp_path):
+    """Sharding by contiguous row ranges + all-gather reproduces the unsharded result (flat
+    block boundaries coincide with the shard boundaries)."""
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, WV_ROOT=ROOT, MASTER_ADDR="127.0.0.1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29531", str(script)],
+                       env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
