@@ -42,6 +42,9 @@ SWEEP = [("Q4_0", 2, 0, 1), ("Q4_1", 3, 0, 1), ("Q5_0", 4, 0, 1), ("Q5_1", 5, 0,
 # Measured per format but outside the timed step (named by the target, not by the sweep config).
 EXTRA = [("AffinePacked_g64", 20, 64, 1), ("BinaryPacked_g32", 19, 32, 1), ("none_f16", 0, 0, 2), ("none_bf16", 0, 0, 3), ("none_f32", 0, 0, 1)]
 NOMINAL_HBM_GBS = 8000.0
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
+# profiles/gemv_tma_q4_0_q8_0_q4_k_full.md (same for both shapes: one launch streams the blob once).
+NCU_DRAM_BYTES = {"Q4_0": 36803840, "Q8_0": 67295232, "Q4_K": 38666752}
 
 
 def measured_hbm_peak():
@@ -285,11 +288,8 @@ def main():
                 per.append({"format": j["name"], "rows": j["rows"], "cols": j["cols"], "packed_bytes": j["bytes"], "us": round(us, 2),
                             "gbs": round(gbs, 1), "frac_measured_peak": round(gbs / peak, 3), "frac_8TBs": round(gbs / NOMINAL_HBM_GBS, 3),
                             "in_step": j in jobs})
-    traffic = None
-    tp = os.path.join(ROOT, "profiles", "traffic.json")
     dom = max((p for p in per if p["in_step"]), key=lambda p: p["us"]) if per else None
-    if dom and os.path.exists(tp):
-        traffic = json.load(open(tp)).get(f'{dom["format"]}_{dom["rows"]}x{dom["cols"]}')
+    traffic = NCU_DRAM_BYTES.get(dom["format"]) if dom else None
 
     # ---- end to end through the host-pointer plugin call
     xh = {c: xs[c].cpu().numpy() for c in xs}
