@@ -100,6 +100,16 @@ int wv_pack(int format, int dtype, int block_weights, const float* w, int rows, 
 int wv_pack_upload_dev(uint64_t key, int format, int dtype, int block_weights, const float* d_w,
                        int rows, int cols, void* stream);
 
+/* No counterpart in the reference. wv_matvec_dev for callers that can no longer allocate
+ * device memory (a serving process that has committed all of HBM to its own pools, or a decode
+ * loop that cannot take the device-wide synchronisation of cudaMalloc): batch-1 y = W x with the
+ * activation scratch in a fixed array inside the library instead of the cudaMalloc'ed arena.
+ * The call performs no allocation. Limits: packed integer-code formats (not IQ4_NL, not
+ * FormatNone), chunk-aligned shapes, in <= 32768 columns (else WV_ESHAPE). The first call on a
+ * device resolves the array's address and should come before any stream capture. All calls
+ * share the array: calls that overlap on the GPU race — keep them on one stream. */
+int wv_matvec_dev_static(uint64_t key, const float* dx, float* dy, int in, int out, void* stream);
+
 /* After the caller has synchronised its stream: 0, or WV_ETIMEOUT when a bounded device wait
  * of an asynchronous call (wv_matvec_dev) ran out since the last query. The reference reports
  * device failures through the error of the synchronous call (webgpu/affine_cache.go:439-443). */

@@ -17,7 +17,7 @@ SYMBOLS = [
     "wv_blob_upload", "wv_blob_upload_wire", "wv_blob_upload_shard", "wv_shard_range",
     "wv_blob_has", "wv_blob_evict", "wv_cache_clear", "wv_cache_bytes", "wv_cache_set_limit",
     "wv_blob_info", "wv_matvec", "wv_matvec_dev", "wv_unpack", "wv_unpack_dev",
-    "wv_pack_sizes", "wv_pack", "wv_pack_upload_dev", "wv_set_tuning", "wv_set_tma_tuning", "wv_device_status",
+    "wv_pack_sizes", "wv_pack", "wv_pack_upload_dev", "wv_set_tuning", "wv_set_tma_tuning", "wv_device_status", "wv_matvec_dev_static",
 ]
 
 WV_OK, WV_ESHAPE, WV_EFORMAT, WV_ENOMEM, WV_ECUDA, WV_ETIMEOUT, WV_ENOTFOUND, WV_EINIT, WV_EARG = (
@@ -65,6 +65,7 @@ def lib() -> C.CDLL:
         L.wv_blob_info.argtypes = [u64, C.POINTER(i), C.POINTER(i), C.POINTER(u64), C.POINTER(u64), C.POINTER(i)]
         L.wv_matvec.argtypes = [u64, vp, vp, i, i, i]
         L.wv_matvec_dev.argtypes = [u64, vp, vp, i, i, i, vp]
+        L.wv_matvec_dev_static.argtypes = [u64, vp, vp, i, i, vp]
         L.wv_unpack.argtypes = [u64, vp]
         L.wv_unpack_dev.argtypes = [u64, vp, vp]
         L.wv_pack_sizes.argtypes = [i, i, i, i, i, C.POINTER(sz), C.POINTER(sz), C.POINTER(sz)]

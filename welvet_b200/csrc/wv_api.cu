@@ -353,6 +353,16 @@ static int lookup(uint64_t key, Entry* out) {
   return WV_OK;
 }
 
+// Copy of a resident blob's descriptor for entry points implemented in other files.
+int wv_api_get_blob(uint64_t key, WvDevBlob* out) {
+  if (g_device < 0) { wv_set_error("welvet_cuda: wv_init has not bound a device"); return WV_EINIT; }
+  Entry e;
+  int rc = lookup(key, &e);
+  if (rc) return rc;
+  *out = e.blob;
+  return WV_OK;
+}
+
 extern "C" int wv_blob_info(uint64_t key, int* rows, int* cols, uint64_t* wire_bytes, uint64_t* dev_bytes, int* chunked) {
   Entry e;
   int rc = lookup(key, &e);

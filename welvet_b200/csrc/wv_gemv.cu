@@ -530,3 +530,88 @@ int wv_launch_gemv(const WvDevBlob& b, const float* dx, float* dy, int batch, in
   }
   return WV_EFORMAT;
 }
+
+
+// ------------------------------------------------------------------ entry point that allocates nothing
+// Some embedders reach this library at a point where they can no longer allocate device
+// memory: a serving process that has already handed every remaining byte of HBM to its own
+// pools (KV cache, another framework's caching allocator) gets out-of-memory from any later
+// cudaMalloc, and a latency-critical decode loop cannot afford the device-wide synchronisation
+// that cudaMalloc / cudaFree imply. wv_matvec_dev takes its activation scratch from an arena
+// that wv_init obtained with cudaMalloc; this variant of the same GEMV (activation
+// pre-quantisation + register-load integer-dot kernel) keeps that scratch in a fixed array
+// inside the library image instead, so the call itself performs no allocation of any kind.
+//
+// Limits: batch 1, packed integer-code formats (not IQ4_NL, not FormatNone: those kernels use
+// no scratch), chunk-aligned shapes, cols <= WV_STATIC_MAX_COLS. Every GPU that loads the
+// library carries the array (about 148 KB) until the process exits. All calls share it and it
+// keeps the previous call's contents; the pre-quantisation kernel rewrites every record the
+// GEMV reads, so nothing has to be cleared, but two calls that overlap on the GPU (different
+// streams) race on it — issue them on one stream.
+#define WV_STATIC_MAX_COLS 32768
+static __device__ __align__(256) uint4 g_static_xq[9 * ((WV_STATIC_MAX_COLS >> 5) | 1)];
+
+// In host code the name g_static_xq is only a stand-in for the symbol, not a device address;
+// the address a kernel may use comes from cudaGetSymbolAddress, once per device.
+static uint4* g_static_xq_addr[64] = {nullptr};
+
+int wv_api_get_blob(uint64_t key, WvDevBlob* out);  // wv_api.cu
+
+template <int F>
+static int launch_static(const WvDevBlob& b, const float* dx, float* dy, uint4* xq, cudaStream_t st) {
+  constexpr WvFmtInfo fi = wv_fmt_info(F);
+  if constexpr (fi.table || fi.kind == WK_NONE) {
+    wv_set_error("wv_matvec_dev_static: format %d uses no scratch and has no static variant", F);
+    return WV_EFORMAT;
+  } else {
+    constexpr int R = 2, S = 1, D = 2;
+    const int cpr = b.cols >> 5, XS = cpr | 1;
+    const size_t smem = (size_t)QCfg<F>::NREC * XS * 16 + (size_t)2 * (WV_GEMV_THREADS / 32) * R * 4 + 16;
+    auto kern = gemv_idot_kernel<F, R, S, D>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return WV_ECUDA;
+    int rc = launch_xquant<fi.bits_lo>(dx, b.cols, 1, QCfg<F>::INT_MID ? fi.mid : 0, xq, st);
+    if (rc) return rc;
+    int grid = wv_sm_count();
+    if (grid > b.rows) grid = b.rows;
+    cudaError_t e = launch_pdl(kern, dim3(grid, 1), dim3(WV_GEMV_THREADS), smem, st, b, (const uint4*)xq, dy, 0, b.rows);
+    if (e != cudaSuccess) { wv_set_error("wv_matvec_dev_static: launch: %s", cudaGetErrorString(e)); return WV_ECUDA; }
+    return WV_OK;
+  }
+}
+
+// y[out] = W x[in] for a resident blob, device pointers, asynchronous on `stream`; performs no
+// cudaMalloc / cudaFree and calls no allocating routine. The first call on a device resolves
+// the address of the static scratch (cudaGetSymbolAddress with that device current); make that
+// first call before starting any stream capture.
+extern "C" int wv_matvec_dev_static(uint64_t key, const float* dx, float* dy, int in, int out, void* stream) {
+  if (!dx || !dy) { wv_set_error("wv_matvec_dev_static: null pointer"); return WV_EARG; }
+  WvDevBlob b;
+  int rc = wv_api_get_blob(key, &b);
+  if (rc) return rc;
+  if (in != b.cols || out != b.rows) { wv_set_error("wv_matvec_dev_static: size mismatch rows=%d cols=%d in=%d out=%d", b.rows, b.cols, in, out); return WV_ESHAPE; }
+  if (!b.fast) { wv_set_error("wv_matvec_dev_static: cols=%d is not chunk aligned", b.cols); return WV_ESHAPE; }
+  if (b.cols > WV_STATIC_MAX_COLS) {
+    wv_set_error("wv_matvec_dev_static: cols=%d exceeds the static scratch maximum of %d", b.cols, WV_STATIC_MAX_COLS);
+    return WV_ESHAPE;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { wv_set_error("wv_matvec_dev_static: bad device"); return WV_ECUDA; }
+  if (!g_static_xq_addr[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_xq);
+    if (e != cudaSuccess || !p) { wv_set_error("wv_matvec_dev_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e)); return WV_ECUDA; }
+    g_static_xq_addr[dev] = static_cast<uint4*>(p);
+  }
+  uint4* xq = g_static_xq_addr[dev];
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (b.format) {
+#define WV_F(f) case f: return launch_static<f>(b, dx, dy, xq, st);
+  WV_F(WV_Q8_0) WV_F(WV_Q4_0) WV_F(WV_Q4_1) WV_F(WV_Q5_0) WV_F(WV_Q5_1)
+  WV_F(WV_Q2_K) WV_F(WV_Q3_K) WV_F(WV_Q4_K) WV_F(WV_Q5_K) WV_F(WV_Q6_K)
+  WV_F(WV_IQ1_S) WV_F(WV_IQ2_XXS) WV_F(WV_IQ2_XS) WV_F(WV_IQ3_XXS) WV_F(WV_IQ3_S) WV_F(WV_IQ4_NL) WV_F(WV_IQ4_XS)
+  WV_F(WV_TERNARY) WV_F(WV_BINARY) WV_F(WV_AFFINE) WV_F(WV_NONE)
+#undef WV_F
+  }
+  wv_set_error("wv_matvec_dev_static: unknown format %d", b.format);
+  return WV_EFORMAT;
+}
