@@ -210,11 +210,15 @@ def main():
     stream.synchronize()
     graph = None
     if world == 1:
+        # One CUDA graph per step: the 38 GEMV launches. With N > 1 the step is issued as plain
+        # launches: capturing the NCCL all-gathers in a graph made process-group teardown hang
+        # on this stack, and the sharded step is collective-latency bound either way.
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             cur = torch.cuda.current_stream().cuda_stream
             for j in jobs:
                 launch(j, cur)
+    launch_mode = "cuda graph" if graph is not None else "plain"
 
     def run_step():
         if graph is not None:
@@ -254,6 +258,13 @@ def main():
     value = full_bytes / (ms_step * 1e-3) / 1e9
     launches_per_step = len(jobs)   # 4096 / 14336 columns take the TMA-fed kernel: one launch per GEMV
 
+    if world > 1:
+        # tear the process group down on every rank before any rank leaves: a graph that holds
+        # NCCL work and a peer that has already exited make destroy_process_group wait forever
+        graph = None
+        torch.cuda.synchronize()
+        dist.barrier()
+        dist.destroy_process_group()
     if rank != 0:
         return
 
@@ -319,6 +330,7 @@ def main():
                    "weights": "N(0,0.02^2) seed 2", "activations": "N(0,1) seed 1",
                    "l2": "inputs larger than L2: one step streams %.0f MB of distinct packed weights" % (full_bytes / 1e6),
                    "sharding": "rows split evenly across ranks, y all-gathered by NCCL" if world > 1 else "single GPU",
+                   "launch": launch_mode,
                    "pct_of_8TBs": round(100 * value / NOMINAL_HBM_GBS, 1)},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
@@ -338,8 +350,6 @@ def main():
         out["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
                                "sample": f"{len(sample)} formats ({','.join(f[0] for f in sample)}) at 4096x14336, 3 timed passes, SIMD-path caches prebuilt"}
     print(json.dumps(out))
-    if world > 1:
-        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
