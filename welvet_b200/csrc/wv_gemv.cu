@@ -309,76 +309,81 @@ gemv_idot_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, float* __rest
 }
 
 // ------------------------------------------------------------------ FormatNone f32 / f16 / bf16
-// Plain streaming GEMV: warp per R rows, lanes read consecutive 16-byte pieces.
-template <int DT, int R>
-__global__ void __launch_bounds__(WV_GEMV_THREADS, 1)
+// Plain streaming GEMV (the reference's DotTile / DotF16Packed / DotBF16Packed rows,
+// layers/dense/simd.go:201-284): two 512-thread CTAs per SM, a warp owns whole rows, lanes
+// read consecutive 16-byte vectors, U vectors per lane per step with the next step's loads
+// issued before the current step's arithmetic (2*U*512 bytes per warp in flight).
+#define WV_DENSE_THREADS 512
+template <int DT, int U>
+__global__ void __launch_bounds__(WV_DENSE_THREADS, 2)
 gemv_dense_kernel(const WvDevBlob b, const float* __restrict__ x, float* __restrict__ y, int row_begin, int row_end) {
   constexpr int EPV = DT == WV_DT_F32 ? 4 : 8;  // elements per 16-byte vector
-  constexpr int NW = WV_GEMV_THREADS / 32;
+  constexpr int NW = WV_DENSE_THREADS / 32;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* xs = reinterpret_cast<float*>(smem_raw);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float* xb = x + (size_t)blockIdx.y * b.cols;
-  float* yb = y + (size_t)blockIdx.y * b.rows;
-  for (int c = tid; c < b.cols; c += WV_GEMV_THREADS) xs[c] = xb[c];
-  __syncthreads();
-  const int nrows = row_end - row_begin, G = (nrows + R - 1) / R;
-  const int g_lo = (int)(((long long)blockIdx.x * G) / gridDim.x), g_hi = (int)(((long long)(blockIdx.x + 1) * G) / gridDim.x);
+  float* yb = y + (size_t)blockIdx.y * b.rows + row_begin;
+  const int nrows = row_end - row_begin;
+  const int c_lo = (int)(((long long)blockIdx.x * nrows) / gridDim.x), c_hi = (int)(((long long)(blockIdx.x + 1) * nrows) / gridDim.x);
+  const int r_lo = c_lo + (int)(((long long)warp * (c_hi - c_lo)) / NW), r_hi = c_lo + (int)(((long long)(warp + 1) * (c_hi - c_lo)) / NW);
   const int vpr = b.cols / EPV;
-  const uint4* wbase = reinterpret_cast<const uint4*>(b.lo);
-  for (int g = g_lo + warp; g < g_hi; g += NW) {
-    float acc[R];
+  const int steps_per_row = (vpr + 32 * U - 1) / (32 * U);
+  const int nsteps = (r_hi - r_lo) * steps_per_row;
+  const uint4* wbase = reinterpret_cast<const uint4*>(b.lo) + (size_t)row_begin * vpr;
+  auto load_step = [&](uint4 (&w)[U], int step) {
+    const int row = r_lo + step / steps_per_row, v0 = (step % steps_per_row) * 32 * U;
 #pragma unroll
-    for (int r = 0; r < R; r++) acc[r] = 0.f;
-    for (int v0 = 0; v0 < vpr; v0 += 64) {
-      uint4 wv[2][R];
+    for (int u = 0; u < U; u++) {
+      const int v = v0 + u * 32 + lane;
+      w[u] = (step < nsteps && v < vpr) ? __ldg(wbase + (size_t)row * vpr + v) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  uint4 nxt[U];
+  load_step(nxt, 0);   // weights do not depend on the previous kernel
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  for (int c = tid; c < b.cols; c += WV_DENSE_THREADS) xs[c] = xb[c];
+  __syncthreads();
+  float acc = 0.f;
+  for (int step = 0; step < nsteps; step++) {
+    uint4 cur[U];
 #pragma unroll
-      for (int u = 0; u < 2; u++) {
-        const int v = v0 + u * 32 + lane;
+    for (int u = 0; u < U; u++) cur[u] = nxt[u];
+    load_step(nxt, step + 1);
+    const int v0 = (step % steps_per_row) * 32 * U;
 #pragma unroll
-        for (int r = 0; r < R; r++) {
-          int row = g * R + r; row = row < nrows ? row : nrows - 1;
-          wv[u][r] = v < vpr ? __ldg(wbase + (size_t)(row_begin + row) * vpr + v) : make_uint4(0, 0, 0, 0);
-        }
-      }
+    for (int u = 0; u < U; u++) {
+      const int v = v0 + u * 32 + lane;
+      if (v < vpr) {
+        const float4* xp = reinterpret_cast<const float4*>(xs + (size_t)v * EPV);
+        const float4 xa = xp[0];
+        const uint4 q = cur[u];
+        if constexpr (DT == WV_DT_F32) {
+          acc = fmaf(__uint_as_float(q.x), xa.x, acc); acc = fmaf(__uint_as_float(q.y), xa.y, acc);
+          acc = fmaf(__uint_as_float(q.z), xa.z, acc); acc = fmaf(__uint_as_float(q.w), xa.w, acc);
+        } else {
+          const float4 xc = xp[1];
+          const unsigned ws[4] = {q.x, q.y, q.z, q.w};
+          const float xe[8] = {xa.x, xa.y, xa.z, xa.w, xc.x, xc.y, xc.z, xc.w};
 #pragma unroll
-      for (int u = 0; u < 2; u++) {
-        const int v = v0 + u * 32 + lane;
-        if (v < vpr) {
-          const float4* xp = reinterpret_cast<const float4*>(xs + (size_t)v * EPV);
-          const float4 xa = xp[0];
-          float4 xc = make_float4(0, 0, 0, 0);
-          if constexpr (EPV == 8) xc = xp[1];
-#pragma unroll
-          for (int r = 0; r < R; r++) {
-            const uint4 q = wv[u][r];
-            if constexpr (DT == WV_DT_F32) {
-              acc[r] = fmaf(__uint_as_float(q.x), xa.x, acc[r]); acc[r] = fmaf(__uint_as_float(q.y), xa.y, acc[r]);
-              acc[r] = fmaf(__uint_as_float(q.z), xa.z, acc[r]); acc[r] = fmaf(__uint_as_float(q.w), xa.w, acc[r]);
-            } else {
-              const unsigned ws[4] = {q.x, q.y, q.z, q.w};
-              const float xe[8] = {xa.x, xa.y, xa.z, xa.w, xc.x, xc.y, xc.z, xc.w};
-#pragma unroll
-              for (int i = 0; i < 4; i++) {
-                float f0, f1;
-                if constexpr (DT == WV_DT_BF16) { f0 = __uint_as_float(ws[i] << 16); f1 = __uint_as_float(ws[i] & 0xffff0000u); }
-                else {
-                  f0 = __half2float(__ushort_as_half((unsigned short)(ws[i] & 0xffffu)));
-                  f1 = __half2float(__ushort_as_half((unsigned short)(ws[i] >> 16)));
-                }
-                acc[r] = fmaf(f0, xe[2 * i], acc[r]); acc[r] = fmaf(f1, xe[2 * i + 1], acc[r]);
-              }
+          for (int i = 0; i < 4; i++) {
+            float f0, f1;
+            if constexpr (DT == WV_DT_BF16) { f0 = __uint_as_float(ws[i] << 16); f1 = __uint_as_float(ws[i] & 0xffff0000u); }
+            else {
+              const float2 hf = __half22float2(*reinterpret_cast<const __half2*>(&ws[i]));
+              f0 = hf.x; f1 = hf.y;
             }
+            acc = fmaf(f0, xe[2 * i], acc); acc = fmaf(f1, xe[2 * i + 1], acc);
           }
         }
       }
     }
+    if ((step + 1) % steps_per_row == 0) {
 #pragma unroll
-    for (int r = 0; r < R; r++) {
-#pragma unroll
-      for (int o = 16; o; o >>= 1) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], o);
-      const int row = g * R + r;
-      if (lane == 0 && row < nrows) yb[row_begin + row] = acc[r];
+      for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (lane == 0) yb[r_lo + step / steps_per_row] = acc;
+      acc = 0.f;
     }
   }
 }
@@ -494,19 +499,20 @@ static int launch_format(const WvDevBlob& b, const float* dx, float* dy, int bat
 template <int DT>
 static int launch_dense(const WvDevBlob& b, const float* dx, float* dy, int batch, int rb, int re, cudaStream_t st) {
   size_t smem = (size_t)b.cols * 4 + 16;
-  if (smem > 227 * 1024) return WV_ESHAPE;
-  static bool attr_set = false;
-  auto kern = gemv_dense_kernel<DT, 2>;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return WV_ECUDA;
-    attr_set = true;
+  if (smem > 110 * 1024) { wv_set_error("gemv: cols=%d needs %zu bytes of shared memory for x (max 112640)", b.cols, smem); return WV_ESHAPE; }
+  static unsigned attr_mask = 0;
+  auto kern = gemv_dense_kernel<DT, 4>;
+  int dev = 0; cudaGetDevice(&dev);
+  if (!(attr_mask & (1u << dev))) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024) != cudaSuccess) return WV_ECUDA;
+    attr_mask |= 1u << dev;
   }
-  int grid = g_tune_grid > 0 ? g_tune_grid : sm_count();
-  const int G = (re - rb + 1) / 2;
-  if (grid > G) grid = G;
+  int grid = g_tune_grid > 0 ? g_tune_grid : 2 * sm_count();
+  if (grid > re - rb) grid = re - rb;
   if (grid < 1) grid = 1;
-  kern<<<dim3(grid, batch), WV_GEMV_THREADS, smem, st>>>(b, dx, dy, rb, re);
-  return cudaGetLastError() == cudaSuccess ? WV_OK : WV_ECUDA;
+  cudaError_t e = launch_pdl(kern, dim3(grid, batch), dim3(WV_DENSE_THREADS), smem, st, b, dx, dy, rb, re);
+  if (e != cudaSuccess) { wv_set_error("gemv (dense) launch: %s", cudaGetErrorString(e)); return WV_ECUDA; }
+  return WV_OK;
 }
 
 int wv_launch_gemv(const WvDevBlob& b, const float* dx, float* dy, int batch, int row_begin, int row_end, cudaStream_t st) {

@@ -249,6 +249,8 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
     const float* xc = reinterpret_cast<const float*>(smem + g.x_off) + (size_t)c * 33;
     if constexpr (fi.table) {
       tbl = reinterpret_cast<const float*>(smem + g.red_off) + 2 * g.nrg * g.nwc * 32 + lane;
+#pragma unroll
+      for (int k = 0; k < 8; k++) xfr[k] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (live) {
         const float* xp = xc;
 #pragma unroll
@@ -257,6 +259,13 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
       }
     } else {
       if (live) quantize_chunk<F>(xr, xc);
+      else {
+#pragma unroll
+        for (int t = 0; t < 24; t++) xr.xw[t] = 0u;
+        xr.mt = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < 6; i++) xr.iv[i] = 0;
+      }
     }
   }
   WV_STAMP(2);
@@ -283,7 +292,7 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   };
 
   const unsigned sbase = smem_u32(smem);
-  const LaneOff lo0 = lane_offsets<F>(g, rg * RT, live ? c : 0, b.group);
+  const LaneOff lo0 = lane_offsets<F>(g, rg * RT, live ? c : g.cpr - 1, b.group);
   // Fetch the fragments of tile t from the ring into registers, then hand the stage back.
   auto wait_tile = [&](int t, bool block) -> bool {
     const int s = t % g.nstage;
@@ -307,7 +316,7 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
     a.lo += st; a.hi += st; a.p0 += st; a.p1 += st; a.km += st;
 #pragma unroll
     for (int rr = 0; rr < RT; rr++) {
-      if (live && !dead && rg * RT + rr < nr) load_frag_smem<F>(fr[rr], a);
+      load_frag_smem<F>(fr[rr], a);   // unconditional: rows past the band read stale ring data and are never stored
       a.lo += g.rb[0]; a.hi += g.rb[1]; a.p0 += g.rb[2]; a.p1 += g.rb[3]; a.km += g.rb[4];
     }
     __syncwarp();
@@ -332,11 +341,11 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
 #pragma unroll
     for (int rr = 0; rr < RT; rr++) {
       const int lr = rg * RT + rr;
-      v[rr] = 0.f;
-      if (live && !dead && lr < nr) {
-        if constexpr (fi.table) v[rr] = chunk_value<F>(fr[rr], xfr, make_float2(0.f, 0.f), tbl);
-        else v[rr] = idot_chunk<F>(fr[rr], xr);
-      }
+      // No per-row branch: the RT chunk-rows form one block of independent dependency chains.
+      // Lanes past the last chunk hold zeroed activations and contribute exactly 0.
+      (void)lr;
+      if constexpr (fi.table) v[rr] = chunk_value<F>(fr[rr], xfr, make_float2(0.f, 0.f), tbl);
+      else v[rr] = idot_chunk<F>(fr[rr], xr);
     }
     // Transposing reduction: RT row sums per lane -> every lane ends with the warp total of one
     // row; the lane whose index equals the row's slot (n & 31) keeps it.
