@@ -130,7 +130,7 @@ __device__ __forceinline__ void load_frag_smem(FragT<F>& f, const LaneOff& a) {
   }
 }
 
-template <int F, int RT>
+template <int F, int RT, bool PREFETCH>
 __global__ void __launch_bounds__(TMA_THREADS, 1)
 gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* __restrict__ xf, float* __restrict__ y,
                 int row_begin, int row_end, const TmaGeom g, int* __restrict__ err) {
@@ -323,19 +323,23 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
     if (lane == 0) mbar_arrive(empty_bar(s));  // the fragments are in registers: hand the stage back
   };
 
-  FragT<F> nxt[RT];
-  if (ntiles > 0) { wait_tile(0, true); fetch_tile(nxt, 0); }
+  FragT<F> nxt[PREFETCH ? RT : 1];
+  if constexpr (PREFETCH) { if (ntiles > 0) { wait_tile(0, true); fetch_tile(nxt, 0); } }
   WV_STAMP(3);
   for (int t = 0; t < ntiles; t++) {
-    const int nr = min(g.tr, band - t * g.tr);
     FragT<F> fr[RT];
-#pragma unroll
-    for (int rr = 0; rr < RT; rr++) fr[rr] = nxt[rr];
-    // prefetch the next tile's fragments before computing when they have already landed
     bool fetched = true;
-    if (t + 1 < ntiles) {
-      fetched = wait_tile(t + 1, false);
-      if (fetched) fetch_tile(nxt, t + 1);
+    if constexpr (PREFETCH) {
+#pragma unroll
+      for (int rr = 0; rr < RT; rr++) fr[rr] = nxt[rr];
+      // prefetch the next tile's fragments before computing when they have already landed
+      if (t + 1 < ntiles) {
+        fetched = wait_tile(t + 1, false);
+        if (fetched) fetch_tile(nxt, t + 1);
+      }
+    } else {
+      wait_tile(t, true);
+      fetch_tile(fr, t);
     }
     float v[RT];
 #pragma unroll
@@ -361,6 +365,19 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
       for (int o = 4; o; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
       tot = __shfl_sync(0xffffffffu, tot, (lane & 3) * 8);  // row (lane & 3) lives in lanes [8*(lane&3), +8)
       if ((lane >> 2) == (t & 7)) keep = tot;
+    } else if constexpr (RT == 8) {
+      const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4;
+      float a[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) a[i] = (b4 ? v[4 + i] : v[i]) + __shfl_xor_sync(0xffffffffu, b4 ? v[i] : v[4 + i], 16);
+      float c0 = (b3 ? a[2] : a[0]) + __shfl_xor_sync(0xffffffffu, b3 ? a[0] : a[2], 8);
+      float c1 = (b3 ? a[3] : a[1]) + __shfl_xor_sync(0xffffffffu, b3 ? a[1] : a[3], 8);
+      tot = (b2 ? c1 : c0) + __shfl_xor_sync(0xffffffffu, b2 ? c0 : c1, 4);
+      tot += __shfl_xor_sync(0xffffffffu, tot, 2);
+      tot += __shfl_xor_sync(0xffffffffu, tot, 1);
+      // row r = 4*b4 + 2*b3 + b2 lives in lanes [4r, 4r+4): lane wants row (lane & 7)
+      tot = __shfl_sync(0xffffffffu, tot, ((lane & 4) ? 16 : 0) + ((lane & 2) ? 8 : 0) + ((lane & 1) ? 4 : 0));
+      if ((lane >> 3) == (t & 3)) keep = tot;
     } else if constexpr (RT == 2) {
       const bool b4 = lane & 16;
       tot = b4 ? v[1] : v[0];
@@ -376,7 +393,7 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
       if (lane == (t & 31)) keep = tot;
     }
     if (((t * RT + RT - 1) & 31) == 31) flush(t * RT + RT - 32);
-    if (!fetched) { wait_tile(t + 1, true); fetch_tile(nxt, t + 1); }
+    if constexpr (PREFETCH) { if (!fetched) { wait_tile(t + 1, true); fetch_tile(nxt, t + 1); } }
   }
   if (nslots & 31) flush(nslots & ~31);
   WV_STAMP(4);
@@ -406,7 +423,7 @@ static bool plane_row_bytes(const WvDevBlob& b, unsigned rb[5]) {
 static int g_tma_rt = 0, g_tma_stages = 0;
 extern "C" void wv_set_tma_tuning(int rows_per_group, int stages) { g_tma_rt = rows_per_group; g_tma_stages = stages; }
 
-template <int F, int RT>
+template <int F, int RT, bool PF>
 static int launch_tma(const WvDevBlob& b, const float* dx, float* dy, int batch, int rb_, int re, cudaStream_t st) {
   constexpr WvFmtInfo fi = wv_fmt_info(F);
   TmaGeom g{};
@@ -433,7 +450,7 @@ static int launch_tma(const WvDevBlob& b, const float* dx, float* dy, int batch,
   g.bar_off = align128(g.red_off + 2u * g.nrg * g.nwc * 32 * 4 + (fi.table ? 2048u : 0u));
   const size_t smem = g.bar_off + 2 * TMA_MAX_STAGES * 8;
 
-  auto kern = gemv_tma_kernel<F, RT>;
+  auto kern = gemv_tma_kernel<F, RT, PF>;
   static unsigned attr_mask = 0;
   int dev = 0; cudaGetDevice(&dev);
   if (!(attr_mask & (1u << dev))) {
@@ -452,10 +469,18 @@ static int launch_tma(const WvDevBlob& b, const float* dx, float* dy, int batch,
 template <int F>
 static int launch_tma_format(const WvDevBlob& b, const float* dx, float* dy, int batch, int rb, int re, cudaStream_t st) {
   constexpr WvFmtInfo fi = wv_fmt_info(F);
-  int rt = g_tma_rt ? g_tma_rt : (fi.bits_lo == 8 ? 2 : 4);
-  if (rt == 1) return launch_tma<F, 1>(b, dx, dy, batch, rb, re, st);
-  if (rt == 2) return launch_tma<F, 2>(b, dx, dy, batch, rb, re, st);
-  return launch_tma<F, 4>(b, dx, dy, batch, rb, re, st);
+  // tuning codes: 1, 2, 4 = rows per group with register prefetch of the next tile; 11, 12, 14, 8 = without
+  // measured best everywhere: four rows per group, fragments fetched right before use (a second
+  // fragment set in registers costs more in register pressure than it hides in latency)
+  int rt = g_tma_rt ? g_tma_rt : 14;
+  switch (rt) {
+  case 1: return launch_tma<F, 1, true>(b, dx, dy, batch, rb, re, st);
+  case 2: return launch_tma<F, 2, true>(b, dx, dy, batch, rb, re, st);
+  case 12: return launch_tma<F, 2, false>(b, dx, dy, batch, rb, re, st);
+  case 8: if constexpr (fi.bits_lo < 8) return launch_tma<F, 8, false>(b, dx, dy, batch, rb, re, st); break;
+  }
+  if (rt == 4) return launch_tma<F, 4, true>(b, dx, dy, batch, rb, re, st);
+  return launch_tma<F, 4, false>(b, dx, dy, batch, rb, re, st);
 }
 
 int wv_launch_gemv_tma(const WvDevBlob& b, const float* dx, float* dy, int batch, int row_begin, int row_end, cudaStream_t st) {
