@@ -196,45 +196,43 @@ __device__ __forceinline__ int dp4a_su(unsigned a, unsigned b, int c) {
 
 // Block-fixed-point conversion of one 32-column chunk straight into registers (what
 // xquant_kernel writes to memory for the register-load kernels). xc points at the chunk's 32
-// floats in shared memory. It runs once per kernel, so it is written as rolled loops over the
-// eight code groups (code that executes once must stay small); the 24 words pass through a
-// per-thread local array and are then copied to registers with static indices.
+// floats in shared memory. Fully unrolled so that the 24 limb words are built in registers
+// with independent dependency chains (the rolled version was latency bound).
 template <int F>
 __device__ __forceinline__ void quantize_chunk(XQRegs& x, const float* xc) {
   constexpr WvFmtInfo fi = wv_fmt_info(F);
-  constexpr int BL = fi.bits_lo, CPW = 32 / BL, SPW = 8 / BL;
-  float amax = 0.f, probe = 0.f;
-#pragma unroll 4
-  for (int j = 0; j < 32; j++) { const float v = xc[j]; amax = fmaxf(amax, fabsf(v)); probe = fmaf(v, 0.f, probe); }
+  constexpr int BL = fi.bits_lo;
+  float xv[32];
+#pragma unroll
+  for (int j = 0; j < 32; j++) xv[j] = xc[j];
+  float am[4] = {0.f, 0.f, 0.f, 0.f}, pr[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int j = 0; j < 32; j++) { am[j & 3] = fmaxf(am[j & 3], fabsf(xv[j])); pr[j & 3] = fmaf(xv[j], 0.f, pr[j & 3]); }  // pr: NaN iff any inf / NaN
+  const float amax = fmaxf(fmaxf(am[0], am[1]), fmaxf(am[2], am[3]));
+  const float probe = (pr[0] + pr[1]) + (pr[2] + pr[3]);
   const unsigned eb = (__float_as_uint(amax) >> 23) & 0xffu;
   float sf = 0.f, inv = 0.f;
   if (probe != 0.f || eb == 255u) sf = __uint_as_float(0x7fc00000u);  // inf / NaN in x: results become NaN
   else if (eb >= 22u) { sf = __uint_as_float((eb - 21u) << 23); inv = __uint_as_float((275u - eb) << 23); }
-  unsigned tmp[24];
   int sl[3][2] = {{0, 0}, {0, 0}, {0, 0}};
 #pragma unroll
-  for (int half = 0; half < 2; half++) {
-    // 1-bit planes split the halves by byte lane instead of by group; they never need the
-    // per-half sums, so everything is accumulated into sl[.][0] for them.
-#pragma unroll 1
-    for (int k = half * 4; k < half * 4 + 4; k++) {
-      const float* p = xc + (k / SPW) * CPW + (k % SPW);   // column of byte lane 0; lane m adds m*SPW
-      // round to nearest integer through the mantissa of 1.5*2^23 + v (|v| <= 2^22): full-rate
-      // FMA + integer subtract instead of the quarter-rate float-to-int conversion
-      const int X0 = __float_as_int(fmaf(p[0], inv, 12582912.0f)) - 0x4B400000, X1 = __float_as_int(fmaf(p[SPW], inv, 12582912.0f)) - 0x4B400000;
-      const int X2 = __float_as_int(fmaf(p[2 * SPW], inv, 12582912.0f)) - 0x4B400000, X3 = __float_as_int(fmaf(p[3 * SPW], inv, 12582912.0f)) - 0x4B400000;
-      const unsigned a01 = __byte_perm(X0, X1, 0x6240), a23 = __byte_perm(X2, X3, 0x6240);   // {b0,b0',b2,b2'}
-      const unsigned w0 = __byte_perm(a01, a23, 0x5410), w2 = __byte_perm(a01, a23, 0x7632);
-      const unsigned w1 = __byte_perm(__byte_perm(X0, X1, 0x0051), __byte_perm(X2, X3, 0x0051), 0x5410);
-      tmp[k] = w0; tmp[8 + k] = w1; tmp[16 + k] = w2;
-      const int hh = BL == 1 ? 0 : half;
-      sl[0][hh] = dp4a_uu(w0, 0x01010101u, sl[0][hh]);
-      sl[1][hh] = dp4a_uu(w1, 0x01010101u, sl[1][hh]);
-      sl[2][hh] = dp4a_su(w2, 0x01010101u, sl[2][hh]);
-    }
-  }
+  for (int k = 0; k < 8; k++) {
+    int X[4];
+    // round to nearest integer through the mantissa of 1.5*2^23 + v (|v| <= 2^22): full-rate
+    // FMA + integer subtract instead of the quarter-rate float-to-int conversion
 #pragma unroll
-  for (int t = 0; t < 24; t++) x.xw[t] = tmp[t];
+    for (int m = 0; m < 4; m++) X[m] = __float_as_int(fmaf(xv[WvLane<BL>::j_of(k, m)], inv, 12582912.0f)) - 0x4B400000;
+    const unsigned a01 = __byte_perm(X[0], X[1], 0x6240), a23 = __byte_perm(X[2], X[3], 0x6240);   // {b0,b0',b2,b2'}
+    const unsigned w0 = __byte_perm(a01, a23, 0x5410), w2 = __byte_perm(a01, a23, 0x7632);
+    const unsigned w1 = __byte_perm(__byte_perm(X[0], X[1], 0x0051), __byte_perm(X[2], X[3], 0x0051), 0x5410);
+    x.xw[k] = w0; x.xw[8 + k] = w1; x.xw[16 + k] = w2;
+    // 1-bit planes split the halves by byte lane instead of by group; they never need the
+    // per-half sums, so everything goes to half 0 for them.
+    const int hh = (BL == 1 || k < 4) ? 0 : 1;
+    sl[0][hh] = dp4a_uu(w0, 0x01010101u, sl[0][hh]);
+    sl[1][hh] = dp4a_uu(w1, 0x01010101u, sl[1][hh]);
+    sl[2][hh] = dp4a_su(w2, 0x01010101u, sl[2][hh]);
+  }
   const int sx0 = sl[0][0] + (sl[1][0] << 8) + (sl[2][0] << 16), sx1 = sl[0][1] + (sl[1][1] << 8) + (sl[2][1] << 16);
   x.mt = make_float4(sf, sf * (float)(sx0 + sx1), sf * (float)sx0, sf * (float)sx1);
 #pragma unroll
@@ -259,10 +257,10 @@ __device__ __forceinline__ float idot_chunk(const FragT<F>& f, const XQRegs& x) 
   constexpr unsigned MASKH = BH ? (0x01010101u * ((1u << BH) - 1u)) << BL : 0u;
   constexpr bool HALVES = QCfg<F>::HALVES;
   constexpr int NH = QCfg<F>::NH;
-  // accumulators [limb][half][parity]: two independent chains per sum keep the dp4a pipe fed
-  int I[3][2][2];
+  // accumulators [limb][half]; the rows a warp processes together supply the independent chains
+  int I[3][2];
 #pragma unroll
-  for (int l = 0; l < 3; l++) { I[l][0][0] = x.iv[l * 2]; I[l][1][0] = HALVES ? x.iv[l * 2 + 1] : 0; I[l][0][1] = 0; I[l][1][1] = 0; }
+  for (int l = 0; l < 3; l++) { I[l][0] = x.iv[l * 2]; I[l][1] = HALVES ? x.iv[l * 2 + 1] : 0; }
 #pragma unroll
   for (int k = 0; k < 8; k++) {
     const int w = k / SPW, sh = k % SPW;
@@ -274,16 +272,18 @@ __device__ __forceinline__ float idot_chunk(const FragT<F>& f, const XQRegs& x) 
       bytes |= hv & MASKH;
     }
     const int h = (HALVES && k >= 4) ? 1 : 0;  // first / second 16 weights of the chunk
-    const int p = k & 1;
-    I[0][h][p] = dp4a_uu(bytes, x.xw[k], I[0][h][p]);
-    I[1][h][p] = dp4a_uu(bytes, x.xw[8 + k], I[1][h][p]);
-    I[2][h][p] = dp4a_us(bytes, x.xw[16 + k], I[2][h][p]);
+    I[0][h] = dp4a_uu(bytes, x.xw[k], I[0][h]);
+    I[1][h] = dp4a_uu(bytes, x.xw[8 + k], I[1][h]);
+    I[2][h] = dp4a_us(bytes, x.xw[16 + k], I[2][h]);
   }
+  // |sum (code - mid) X| <= 15 * 32 * 2^22 < 2^31 for codes of at most 4 bits: recombine the limbs
+  // in integer arithmetic and convert once; wider codes recombine in f32.
+  constexpr bool SMALL = (BL + BH) <= 4;
   float val[2];
 #pragma unroll
   for (int h = 0; h < NH; h++) {
-    const int i0 = I[0][h][0] + I[0][h][1], i1 = I[1][h][0] + I[1][h][1], i2 = I[2][h][0] + I[2][h][1];
-    val[h] = fmaf(65536.0f, (float)i2, (float)(i0 + (i1 << 8)));
+    if constexpr (SMALL) val[h] = (float)(I[0][h] + (I[1][h] << 8) + (I[2][h] << 16));
+    else val[h] = fmaf(65536.0f, (float)I[2][h], (float)(I[0][h] + (I[1][h] << 8)));
   }
   const float4 mt = x.mt;
   float v, extra = 0.f;

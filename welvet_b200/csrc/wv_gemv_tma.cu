@@ -16,9 +16,14 @@
 //     stops issuing copies, drains the ones in flight (bounded again) and returns.
 #include "wv_gemv_common.cuh"
 
+#ifndef TMA_CONSUMER_WARPS
 #define TMA_CONSUMER_WARPS 16
+#endif
 #define TMA_THREADS ((TMA_CONSUMER_WARPS + 1) * 32)
 #define TMA_MAX_STAGES 8
+#ifndef TMA_MAX_ROW_GROUPS
+#define TMA_MAX_ROW_GROUPS 8
+#endif
 #define TMA_SPIN_LIMIT (1u << 22)
 
 struct TmaGeom {
@@ -30,6 +35,7 @@ struct TmaGeom {
   unsigned stage_bytes;
   unsigned off[5];   // lo, hi, p0, p1, km section offsets inside a stage
   unsigned rb[5];    // bytes per row of each plane (0 = plane absent)
+  int rows_base, rows_rem;  // CTA b owns rows_base (+1 if b < rows_rem) consecutive rows
   unsigned x_off;    // staged activations: 33 floats per chunk (32 + one of padding)
   unsigned red_off;  // float red[2][nrg][nwc][32]
   unsigned bar_off;  // full[nstage], empty[nstage]
@@ -139,10 +145,12 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int s_abort;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int nrows = row_end - row_begin;
-  const int c_lo = (int)(((long long)blockIdx.x * nrows) / gridDim.x), c_hi = (int)(((long long)(blockIdx.x + 1) * nrows) / gridDim.x);
-  const int band = c_hi - c_lo;
+  // band of this CTA without divisions: the host splits the rows as evenly as possible
+  const int bid = blockIdx.x;
+  const int band = g.rows_base + (bid < g.rows_rem ? 1 : 0);
+  const int c_lo = bid * g.rows_base + min(bid, g.rows_rem), c_hi = c_lo + band;
   const int ntiles = (band + g.tr - 1) / g.tr;
+  (void)row_end;
   const unsigned bar0 = smem_u32(smem + g.bar_off);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (g.nstage + s); };
@@ -167,10 +175,13 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
     const void* src[5] = {b.lo, b.hi, b.p0, b.p1, b.km};
     bool dead = false;
     int issued = 0;
+    int ps = 0;            // stage of the tile being issued
+    unsigned ppar = 1;     // parity of the "empty" phase to wait for once the ring has wrapped
+    bool wrapped = false;
     auto issue_tile = [&](int t) {
-      const int s = t % g.nstage;
-      if (t >= g.nstage) {
-        if (*(volatile int*)&s_abort || !mbar_wait(empty_bar(s), ((t / g.nstage) - 1) & 1)) {
+      const int s = ps;
+      if (wrapped) {
+        if (*(volatile int*)&s_abort || !mbar_wait(empty_bar(s), ppar)) {
           if (!*(volatile int*)&s_abort) { atomicCAS_system(err, 0, 100 + s); *(volatile int*)&s_abort = 1; }
           dead = true;
           return;
@@ -188,6 +199,7 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
         if (g.rb[i]) bulk_g2s(dst + g.off[i], (const unsigned char*)src[i] + (size_t)(row_begin + r0) * g.rb[i], g.rb[i] * nr, full_bar(s));
       }
       issued = t + 1;
+      if (++ps == g.nstage) { ps = 0; wrapped = true; ppar ^= 1u; }
     };
     if (lane == 0 && ntiles > 0) issue_tile(0);
     __syncwarp();
@@ -241,6 +253,7 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
     }
   }
   asm volatile("bar.sync 15, %0;" ::"n"(TMA_CONSUMER_WARPS * 32) : "memory");
+  WV_STAMP(5);
   if (rg >= g.nrg) return;
   XQRegs xr;
   float4 xfr[8];
@@ -294,25 +307,26 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   const unsigned sbase = smem_u32(smem);
   const LaneOff lo0 = lane_offsets<F>(g, rg * RT, live ? c : g.cpr - 1, b.group);
   // Fetch the fragments of tile t from the ring into registers, then hand the stage back.
-  auto wait_tile = [&](int t, bool block) -> bool {
-    const int s = t % g.nstage;
+  // stage index and phase parity of the tile being fetched, advanced incrementally (no divisions
+  // in the loop)
+  int fs = 0;
+  unsigned fpar = 0;
+  auto wait_tile = [&](bool block) -> bool {
     if (dead || *(volatile int*)&s_abort) { dead = true; return true; }
     if (!block) {
       unsigned ok;
       asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                   : "=r"(ok) : "r"(full_bar(s)), "r"((unsigned)((t / g.nstage) & 1)) : "memory");
+                   : "=r"(ok) : "r"(full_bar(fs)), "r"(fpar) : "memory");
       return __all_sync(0xffffffffu, ok != 0);
     }
-    if (!mbar_wait(full_bar(s), (t / g.nstage) & 1)) {
-      atomicCAS_system(err, 0, 300 + s); *(volatile int*)&s_abort = 1; dead = true;
+    if (!mbar_wait(full_bar(fs), fpar)) {
+      atomicCAS_system(err, 0, 300 + fs); *(volatile int*)&s_abort = 1; dead = true;
     }
     return true;
   };
-  auto fetch_tile = [&](FragT<F> (&fr)[RT], int t) {
-    const int s = t % g.nstage;
-    const int nr = min(g.tr, band - t * g.tr);
+  auto fetch_tile = [&](FragT<F> (&fr)[RT]) {
     LaneOff a = lo0;
-    const unsigned st = sbase + (unsigned)s * g.stage_bytes;
+    const unsigned st = sbase + (unsigned)fs * g.stage_bytes;
     a.lo += st; a.hi += st; a.p0 += st; a.p1 += st; a.km += st;
 #pragma unroll
     for (int rr = 0; rr < RT; rr++) {
@@ -320,11 +334,12 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
       a.lo += g.rb[0]; a.hi += g.rb[1]; a.p0 += g.rb[2]; a.p1 += g.rb[3]; a.km += g.rb[4];
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive(empty_bar(s));  // the fragments are in registers: hand the stage back
+    if (lane == 0) mbar_arrive(empty_bar(fs));  // the fragments are in registers: hand the stage back
+    if (++fs == g.nstage) { fs = 0; fpar ^= 1u; }
   };
 
   FragT<F> nxt[PREFETCH ? RT : 1];
-  if constexpr (PREFETCH) { if (ntiles > 0) { wait_tile(0, true); fetch_tile(nxt, 0); } }
+  if constexpr (PREFETCH) { if (ntiles > 0) { wait_tile(true); fetch_tile(nxt); } }
   WV_STAMP(3);
   for (int t = 0; t < ntiles; t++) {
     FragT<F> fr[RT];
@@ -334,12 +349,12 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
       for (int rr = 0; rr < RT; rr++) fr[rr] = nxt[rr];
       // prefetch the next tile's fragments before computing when they have already landed
       if (t + 1 < ntiles) {
-        fetched = wait_tile(t + 1, false);
-        if (fetched) fetch_tile(nxt, t + 1);
+        fetched = wait_tile(false);
+        if (fetched) fetch_tile(nxt);
       }
     } else {
-      wait_tile(t, true);
-      fetch_tile(fr, t);
+      wait_tile(true);
+      fetch_tile(fr);
     }
     float v[RT];
 #pragma unroll
@@ -393,7 +408,7 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
       if (lane == (t & 31)) keep = tot;
     }
     if (((t * RT + RT - 1) & 31) == 31) flush(t * RT + RT - 32);
-    if constexpr (PREFETCH) { if (!fetched) { wait_tile(t + 1, true); fetch_tile(nxt, t + 1); } }
+    if constexpr (PREFETCH) { if (!fetched) { wait_tile(true); fetch_tile(nxt); } }
   }
   if (nslots & 31) flush(nslots & ~31);
   WV_STAMP(4);
@@ -432,7 +447,7 @@ static int launch_tma(const WvDevBlob& b, const float* dx, float* dy, int batch,
   g.nwc = (g.cpr + 31) / 32;
   if (g.nwc > TMA_CONSUMER_WARPS) return 1;
   g.nrg = TMA_CONSUMER_WARPS / g.nwc;
-  if (g.nrg > 8) g.nrg = 8;
+  if (g.nrg > TMA_MAX_ROW_GROUPS) g.nrg = TMA_MAX_ROW_GROUPS;
   g.tr = g.nrg * RT;
   unsigned off = 0;
   for (int i = 0; i < 5; i++) { g.off[i] = off; off = align128(off + g.rb[i] * g.tr); }
@@ -460,6 +475,8 @@ static int launch_tma(const WvDevBlob& b, const float* dx, float* dy, int batch,
   int grid = wv_sm_count();
   const int nrows = re - rb_;
   if (grid > nrows) grid = nrows;
+  g.rows_base = nrows / grid;
+  g.rows_rem = nrows % grid;
   const uint4* xq = nullptr;  // activations are quantised inside the kernel
   cudaError_t e = launch_pdl(kern, dim3(grid, batch), dim3(TMA_THREADS), smem, st, b, xq, dx, dy, rb_, re, g, g_err_dev);
   if (e != cudaSuccess) { wv_set_error("gemv (tma) launch: %s", cudaGetErrorString(e)); return WV_ECUDA; }
