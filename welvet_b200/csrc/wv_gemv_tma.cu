@@ -15,6 +15,7 @@
 //   * all waits on mbarriers are bounded: when a wait runs out the CTA records an error code,
 //     stops issuing copies, drains the ones in flight (bounded again) and returns.
 #include "wv_gemv_common.cuh"
+#include "wv_tma_common.cuh"
 
 #ifndef TMA_CONSUMER_WARPS
 #define TMA_CONSUMER_WARPS 16
@@ -24,7 +25,6 @@
 #ifndef TMA_MAX_ROW_GROUPS
 #define TMA_MAX_ROW_GROUPS 8
 #endif
-#define TMA_SPIN_LIMIT (1u << 22)
 
 struct TmaGeom {
   int cpr;           // chunks per row
@@ -36,6 +36,7 @@ struct TmaGeom {
   unsigned off[5];   // lo, hi, p0, p1, km section offsets inside a stage
   unsigned rb[5];    // bytes per row of each plane (0 = plane absent)
   int rows_base, rows_rem;  // CTA b owns rows_base (+1 if b < rows_rem) consecutive rows
+  int lead;          // tiles issued before the producer waits for the activation loads to be on their way
   unsigned x_off;    // staged activations: 33 floats per chunk (32 + one of padding)
   unsigned red_off;  // float red[2][nrg][nwc][32]
   unsigned bar_off;  // full[nstage], empty[nstage]
@@ -48,43 +49,14 @@ static int* g_err_dev = nullptr;
 #ifdef WV_PHASES  // development aid: per-CTA clock stamps (start, x ready, first tile ready, end)
 static __device__ long long* g_dbg = nullptr;
 extern "C" void wv_debug_set_buffer(long long* p) { cudaMemcpyToSymbol(g_dbg, &p, sizeof p); }
-#define WV_STAMP(i) do { if (g_dbg && threadIdx.x == 0) g_dbg[blockIdx.x * 8 + (i)] = clock64(); } while (0)
+#define WV_STAMP(i) do { if (g_dbg && threadIdx.x == 0) g_dbg[blockIdx.x * 64 + (i)] = clock64(); } while (0)
+#define WV_STAMP_ANY(i) do { if (g_dbg && (i) < 64) g_dbg[blockIdx.x * 64 + (i)] = clock64(); } while (0)
+#define WV_STAMP_NS(i) do { if (g_dbg && threadIdx.x == 0) { long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_dbg[blockIdx.x * 64 + (i)] = t_; } } while (0)
 #else
 #define WV_STAMP(i) do {} while (0)
+#define WV_STAMP_ANY(i) do {} while (0)
+#define WV_STAMP_NS(i) do {} while (0)
 #endif
-
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(unsigned bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-// Bounded wait: returns false when the phase did not complete within the spin limit.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
-  for (unsigned i = 0; i < TMA_SPIN_LIMIT; i++) {
-    unsigned ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    if (ok) return true;
-  }
-  return false;
-}
-__device__ __forceinline__ void bulk_g2s(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-
-__device__ __forceinline__ unsigned lds32(unsigned a) { unsigned v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
-__device__ __forceinline__ unsigned lds16(unsigned a) { unsigned short v; asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a)); return v; }
-__device__ __forceinline__ uint2 lds64(unsigned a) { uint2 v; asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a)); return v; }
-__device__ __forceinline__ uint4 lds128(unsigned a) { uint4 v; asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a)); return v; }
 
 // Per-lane shared-memory addresses (32-bit) of this lane's chunk in row 0 of its row group,
 // relative to a stage base; a row further down adds the plane's row bytes.
@@ -144,6 +116,7 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   constexpr int BL = fi.bits_lo;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int s_abort;
+  __shared__ unsigned s_xissued;   // consumer warps that have issued their loads of x
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   // band of this CTA without divisions: the host splits the rows as evenly as possible
   const int bid = blockIdx.x;
@@ -158,6 +131,7 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
 
   if (tid == 0) {
     s_abort = 0;
+    s_xissued = 0;
     for (int s = 0; s < g.nstage; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), nactive); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -169,9 +143,7 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
 
   if (warp == TMA_CONSUMER_WARPS) {
     // ------------------------------------------------------------ producer
-    // One thread issues the copies. The whole warp stays convergent around the named barrier
-    // (bar.sync counts whole warps), so the loop is split at the barrier instead of calling
-    // it from inside the single-thread branch.
+    // One thread issues the copies; the other lanes of the warp have nothing to do.
     const void* src[5] = {b.lo, b.hi, b.p0, b.p1, b.km};
     bool dead = false;
     int issued = 0;
@@ -199,15 +171,19 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
         if (g.rb[i]) bulk_g2s(dst + g.off[i], (const unsigned char*)src[i] + (size_t)(row_begin + r0) * g.rb[i], g.rb[i] * nr, full_bar(s));
       }
       issued = t + 1;
+      WV_STAMP_ANY(40 + t);
       if (++ps == g.nstage) { ps = 0; wrapped = true; ppar ^= 1u; }
     };
-    if (lane == 0 && ntiles > 0) issue_tile(0);
-    __syncwarp();
-    // The activation loads must not queue behind a full ring of weight traffic: after the
-    // first tile, hold further copies until every consumer has issued its loads of x.
-    asm volatile("bar.sync 14, %0;" ::"n"(TMA_CONSUMER_WARPS * 32 + 32) : "memory");
     if (lane == 0) {
-      for (int t = 1; t < ntiles && !dead; t++) issue_tile(t);
+      int t = 0;
+      for (; t < ntiles && t < g.lead && !dead; t++) issue_tile(t);
+      // The activation loads must not queue behind a full ring of weight traffic: after the
+      // first tiles, hold further copies until every consumer warp has issued its loads of x
+      // (a relaxed counter: a barrier here would wait for the loads to complete).
+      for (unsigned i = 0; i < TMA_SPIN_LIMIT; i++) {
+        if (*(volatile unsigned*)&s_xissued >= TMA_CONSUMER_WARPS) break;
+      }
+      for (; t < ntiles && !dead; t++) issue_tile(t);
       // drain: every copy issued must have landed before the CTA gives its shared memory back
       for (int t = max(0, issued - g.nstage); t < issued; t++) {
         if (!mbar_wait(full_bar(t % g.nstage), (t / g.nstage) & 1)) { atomicCAS_system(err, 0, 200 + t % g.nstage); break; }
@@ -222,6 +198,7 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   const bool live = c < g.cpr;
 
   WV_STAMP(0);
+  WV_STAMP_NS(6);
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   WV_STAMP(1);
@@ -241,14 +218,14 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
         const int i = tid + u * TMA_CONSUMER_WARPS * 32;
         if (i < nv) v[u] = __ldg(reinterpret_cast<const float4*>(xrow) + i);
       }
-      asm volatile("bar.arrive 14, %0;" ::"n"(TMA_CONSUMER_WARPS * 32 + 32) : "memory");
+      if (lane == 0) asm volatile("red.relaxed.cta.shared::cta.add.u32 [%0], 1;" ::"r"(smem_u32(&s_xissued)) : "memory");
 #pragma unroll
       for (int u = 0; u < 8; u++) {
         const int i = tid + u * TMA_CONSUMER_WARPS * 32;
         if (i < nv) { float* d = xs + (i >> 3) * 33 + (i & 7) * 4; d[0] = v[u].x; d[1] = v[u].y; d[2] = v[u].z; d[3] = v[u].w; }
       }
     } else {
-      asm volatile("bar.arrive 14, %0;" ::"n"(TMA_CONSUMER_WARPS * 32 + 32) : "memory");
+      if (lane == 0) asm volatile("red.relaxed.cta.shared::cta.add.u32 [%0], 1;" ::"r"(smem_u32(&s_xissued)) : "memory");
       for (int i = tid; i < b.cols; i += TMA_CONSUMER_WARPS * 32) xs[(i >> 5) * 33 + (i & 31)] = __ldg(xrow + i);
     }
   }
@@ -354,6 +331,7 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
       }
     } else {
       wait_tile(true);
+      WV_STAMP(8 + 2 * t);
       fetch_tile(fr);
     }
     float v[RT];
@@ -408,10 +386,12 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
       if (lane == (t & 31)) keep = tot;
     }
     if (((t * RT + RT - 1) & 31) == 31) flush(t * RT + RT - 32);
+    WV_STAMP(9 + 2 * t);
     if constexpr (PREFETCH) { if (!fetched) { wait_tile(true); fetch_tile(nxt); } }
   }
   if (nslots & 31) flush(nslots & ~31);
   WV_STAMP(4);
+  WV_STAMP_NS(7);
 }
 
 // ------------------------------------------------------------------ host side
@@ -437,6 +417,7 @@ static bool plane_row_bytes(const WvDevBlob& b, unsigned rb[5]) {
 
 static int g_tma_rt = 0, g_tma_stages = 0;
 extern "C" void wv_set_tma_tuning(int rows_per_group, int stages) { g_tma_rt = rows_per_group; g_tma_stages = stages; }
+int wv_tma_tuning_stages() { return g_tma_stages; }
 
 template <int F, int RT, bool PF>
 static int launch_tma(const WvDevBlob& b, const float* dx, float* dy, int batch, int rb_, int re, cudaStream_t st) {
@@ -458,7 +439,8 @@ static int launch_tma(const WvDevBlob& b, const float* dx, float* dy, int batch,
   if (g.stage_bytes * 2 + fixed > avail) return 1;
   int ns = (int)((avail - fixed) / g.stage_bytes);
   if (ns > TMA_MAX_STAGES) ns = TMA_MAX_STAGES;
-  if (g_tma_stages > 1 && g_tma_stages < ns) ns = g_tma_stages;
+  if (g_tma_stages % 100 > 1 && g_tma_stages % 100 < ns) ns = g_tma_stages % 100;
+  g.lead = g_tma_stages >= 100 ? g_tma_stages / 100 : 1;
   g.nstage = ns;
   g.x_off = g.stage_bytes * ns;
   g.red_off = g.x_off + xbytes;
@@ -489,7 +471,7 @@ static int launch_tma_format(const WvDevBlob& b, const float* dx, float* dy, int
   // tuning codes: 1, 2, 4 = rows per group with register prefetch of the next tile; 11, 12, 14, 8 = without
   // measured best everywhere: four rows per group, fragments fetched right before use (a second
   // fragment set in registers costs more in register pressure than it hides in latency)
-  int rt = g_tma_rt ? g_tma_rt : 14;
+  int rt = (g_tma_rt && g_tma_rt < 20) ? g_tma_rt : 14;
   switch (rt) {
   case 1: return launch_tma<F, 1, true>(b, dx, dy, batch, rb, re, st);
   case 2: return launch_tma<F, 2, true>(b, dx, dy, batch, rb, re, st);
@@ -501,6 +483,13 @@ static int launch_tma_format(const WvDevBlob& b, const float* dx, float* dy, int
 }
 
 int wv_launch_gemv_tma(const WvDevBlob& b, const float* dx, float* dy, int batch, int row_begin, int row_end, cudaStream_t st) {
+  // tuning codes 21, 22, 24 send the formats with one parameter group per chunk to the tensor-pipe
+  // kernel (the digit is its chunk pairs per warp); it measures level with the dp4a kernel so far
+  // and is not the default
+  if (g_tma_rt >= 20) {
+    const int rc = wv_launch_gemv_mma(b, dx, dy, batch, row_begin, row_end, st, g_tma_rt - 20);
+    if (rc != 1) return rc;
+  }
   switch (b.format) {
 #define WV_F(f) case f: return launch_tma_format<f>(b, dx, dy, batch, row_begin, row_end, st);
   WV_F(WV_Q8_0) WV_F(WV_Q4_0) WV_F(WV_Q4_1) WV_F(WV_Q5_0) WV_F(WV_Q5_1)
@@ -519,6 +508,7 @@ int wv_tma_take_error() {
   if (v) *(volatile int*)g_err_host = 0;
   return v;
 }
+int* wv_tma_err_ptr() { return g_err_dev; }
 int wv_tma_init() {
   if (g_err_host) return WV_OK;
   if (cudaHostAlloc(&g_err_host, sizeof(int), cudaHostAllocMapped) != cudaSuccess) { cudaGetLastError(); return WV_ENOMEM; }
