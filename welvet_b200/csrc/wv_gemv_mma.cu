@@ -69,13 +69,22 @@ __device__ __forceinline__ void mma_u8u8(int (&c)[4], unsigned a0, unsigned a1, 
   asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void mma_s8u8(int (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 __device__ __forceinline__ void sts128(unsigned a, unsigned x, unsigned y, unsigned z, unsigned w) {
   asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
 
 template <int F> struct MmaCfg {
   static constexpr WvFmtInfo fi = wv_fmt_info(F);
-  static constexpr bool INT_MID = fi.mid != 0 && !fi.half_mid;
+  // Q4_0 / Q8_0 store code ^ mid, i.e. the reference's own two's-complement code with the top bit
+  // flipped: flipping it back yields the signed code (times 16 for the nibbles, which sit in the
+  // high half of their byte), so these formats multiply signed codes and need no -mid start value.
+  static constexpr bool SIGNED_A = F == WV_Q4_0 || F == WV_Q8_0;
+  static constexpr float A_SCALE = F == WV_Q4_0 ? 1.0f / 16.0f : 1.0f;
+  static constexpr bool INT_MID = fi.mid != 0 && !fi.half_mid && !SIGNED_A;
   static constexpr bool USES_SX = fi.has_min || fi.sign || fi.half_mid;
   static constexpr bool OK = !fi.table && fi.pgroup != 16 && fi.kind != WK_KQUANT && fi.kind != WK_TERNARY &&
                              fi.kind != WK_NONE && fi.bits_hi <= 1;
@@ -140,7 +149,7 @@ __device__ __forceinline__ void mma_quantize_slot(unsigned slot) {
     constexpr float coef = fi.has_min ? 1.0f : (fi.sign ? -1.0f : -((float)fi.mid + 0.5f));
     sx = coef * (sf * tot);
   }
-  const float f0 = fi.sign ? 2.0f * sf : sf;
+  const float f0 = (fi.sign ? 2.0f * sf : sf) * MmaCfg<F>::A_SCALE;
   if constexpr (!MmaCfg<F>::INT_MID) sts128(slot + MMA_SLOT_K, 0u, 0u, 0u, 0u);
   sts128(slot + MMA_SLOT_META, __float_as_uint(f0), __float_as_uint(f0 * 65536.0f), __float_as_uint(sx), 0u);
 }
@@ -156,14 +165,14 @@ __device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap* tm,
                ::"r"(dst), "l"(reinterpret_cast<unsigned long long>(tm)), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
 }
 
-template <int F, int PW>
+template <int F, int PW, int NSEG>
 __global__ void __launch_bounds__(MMA_THREADS, 1)
 gemv_mma_kernel(const WvDevBlob b, const float* __restrict__ xf, float* __restrict__ y, int row_begin, const MmaGeom g,
                 int* __restrict__ err, const __grid_constant__ CUtensorMap tm_lo, const __grid_constant__ CUtensorMap tm_hi,
                 const __grid_constant__ CUtensorMap tm_p0, const __grid_constant__ CUtensorMap tm_p1) {
   constexpr WvFmtInfo fi = wv_fmt_info(F);
   constexpr int BL = fi.bits_lo, BH = fi.bits_hi;
-  constexpr bool INT_MID = MmaCfg<F>::INT_MID;
+  constexpr bool INT_MID = MmaCfg<F>::INT_MID, SIGNED_A = MmaCfg<F>::SIGNED_A;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ int s_abort;
   __shared__ unsigned s_xissued;   // consumer warps that have issued their loads of x
@@ -243,13 +252,11 @@ gemv_mma_kernel(const WvDevBlob b, const float* __restrict__ xf, float* __restri
   const int gr = lane >> 2, p = lane & 3, sel = p >> 1, part = p & 1;
   const int mulp = part ? -64 : 256;
   // B operand: lanes 0-15 carry columns 0..3 (chunk A: three digit columns and the ones), lanes
-  // 16-31 columns 4..7 (chunk B); the other half of the warp reads zeros.
-  const unsigned zeros = g.const_off, ones = zeros + 16u + (unsigned)p * 8u;   // offsets from the aligned base
+  // 16-31 columns 4..7 (chunk B). A lane keeps the words of its own chunk of every pair in
+  // registers (loaded once after quantisation) and presents zeros for the other chunk.
   const int ncol = gr & 3;
-  const unsigned dig = g.x_off + (unsigned)ncol * 32u + (unsigned)p * 8u;
-  unsigned bA_base, bA_str, bB_base, bB_str;
-  if (lane < 16) { bA_base = ncol < 3 ? dig : ones; bA_str = ncol < 3 ? MMA_SLOT : 0u; bB_base = zeros; bB_str = 0u; }
-  else { bB_base = ncol < 3 ? dig : ones; bB_str = ncol < 3 ? MMA_SLOT : 0u; bA_base = zeros; bA_str = 0u; }
+  const unsigned dig = g.x_off + (unsigned)ncol * 32u + (unsigned)p * 8u;   // offset from the aligned base
+  const unsigned maskA = lane < 16 ? 0xffffffffu : 0u, maskB = ~maskA;
   // A operand: this lane's word inside a chunk's lo / hi data and the shifts that bring its two
   // code groups (2p, 2p+1) down to bit 0
   const unsigned lo_lane = BL == 8 ? p * 8u : (BL == 4 ? p * 4u : (BL == 2 ? (p >> 1) * 4u : 0u));
@@ -263,8 +270,13 @@ gemv_mma_kernel(const WvDevBlob b, const float* __restrict__ xf, float* __restri
   auto ld64 = [&](unsigned o) { return *reinterpret_cast<const uint2*>(smem + o); };
   auto ldf = [&](unsigned o) { return *reinterpret_cast<const float*>(smem + o); };
   auto load_a = [&](unsigned lo_o, unsigned hi_o, unsigned& q0, unsigned& q1) {
-    if constexpr (BL == 8) { const uint2 w = ld64(lo_o); q0 = w.x; q1 = w.y; }
-    else {
+    if constexpr (BL == 8) {
+      const uint2 w = ld64(lo_o);
+      q0 = SIGNED_A ? w.x ^ 0x80808080u : w.x; q1 = SIGNED_A ? w.y ^ 0x80808080u : w.y;
+    } else if constexpr (SIGNED_A) {   // 4-bit: signed code * 16 in each byte
+      const unsigned w = ld32(lo_o);
+      q0 = ((w << 4) & 0xF0F0F0F0u) ^ 0x80808080u; q1 = (w & 0xF0F0F0F0u) ^ 0x80808080u;
+    } else {
       const unsigned w = ld32(lo_o) >> sh_lo;
       q0 = w & MASK; q1 = (w >> BL) & MASK;
     }
@@ -322,6 +334,24 @@ gemv_mma_kernel(const WvDevBlob b, const float* __restrict__ xf, float* __restri
   if (tid < g.cpr) mma_quantize_slot<F>(xs0 + (unsigned)tid * MMA_SLOT);
   asm volatile("bar.sync 15, %0;" ::"n"(MMA_WARPS * 32) : "memory");
   MSTAMP(2);
+  // this lane's B words and scale factor for each of its NSEG * PW chunk pairs
+  // (the factors stay in shared memory when there are too many pairs for the register file)
+  constexpr bool FR_REGS = NSEG * PW <= 8;
+  unsigned bo0[NSEG * PW], bo1[NSEG * PW];
+  float fr[FR_REGS ? NSEG * PW : 1];
+#pragma unroll
+  for (int sg = 0; sg < NSEG; sg++) {
+#pragma unroll
+    for (int i = 0; i < PW; i++) {
+      const int jg = sg * (32 * PW) + wq + 2 * i;                 // chunk A of the pair
+      const int jb = jg + (lane < 16 ? 0 : 1), js = jg + sel;
+      uint2 w = make_uint2(0x01010101u, 0x01010101u);            // column 3 / 7: ones
+      if (ncol < 3) w = jb < g.cpr ? ld64(dig + (unsigned)jb * MMA_SLOT) : make_uint2(0u, 0u);
+      bo0[sg * PW + i] = w.x; bo1[sg * PW + i] = w.y;
+      if constexpr (FR_REGS) fr[sg * PW + i] = js < g.cpr ? ldf(g.x_off + (unsigned)js * MMA_SLOT + MMA_SLOT_META + (unsigned)part * 4u) : 0.f;
+      (void)js;
+    }
+  }
 
   float* red = reinterpret_cast<float*>(smem + g.red_off);
   float* yb = y + (size_t)blockIdx.y * b.rows + row_begin + c_lo;
@@ -330,18 +360,19 @@ gemv_mma_kernel(const WvDevBlob b, const float* __restrict__ xf, float* __restri
   bool dead = false;
   for (int mt = 0; mt < nmt; mt++) {
     float acc0 = 0.f, acc1 = 0.f;
-    for (int seg = 0; seg < g.nseg; seg++) {
+#pragma unroll
+    for (int seg = 0; seg < NSEG; seg++) {
       if (!dead) {
         if (*(volatile int*)&s_abort) dead = true;
         else if (!mbar_wait(full_bar(fs), fpar)) { atomicCAS_system(err, 0, 600 + fs); *(volatile int*)&s_abort = 1; dead = true; }
       }
-      MSTAMP(8 + 2 * (mt * g.nseg + seg));
+      MSTAMP(8 + 2 * (mt * NSEG + seg));
       const unsigned st = (unsigned)fs * g.stage_bytes;   // offset of the stage from the aligned base
-      const int jseg = seg * g.seg_chunks + wq;   // slot index of this warp's first chunk in the segment
+      const int jseg = seg * (32 * PW) + wq;   // slot index of this warp's first chunk in the segment
 #pragma unroll
       for (int i = 0; i < PW; i++) {
-        // chunk A; chunk B = jg + 1. Pairs past the end of the row (last segment only) read
-        // zero-filled codes and scales, so with any real slot they contribute exactly 0.
+        // Chunk A = jseg + 2i, chunk B the next one. Pairs past the end of the row (last segment
+        // only) read zero-filled codes and scales and carry zero B words and factors.
         const int jg = min(jseg + 2 * i, g.cpr - 2);
         const unsigned slot = g.x_off + (unsigned)(jg + sel) * MMA_SLOT;
         int c[4] = {0, 0, 0, 0};
@@ -349,19 +380,23 @@ gemv_mma_kernel(const WvDevBlob b, const float* __restrict__ xf, float* __restri
           const uint2 kk = ld64(slot + MMA_SLOT_K + (unsigned)part * 8u);
           c[0] = (int)kk.x; c[1] = (int)kk.y; c[2] = (int)kk.x; c[3] = (int)kk.y;
         }
+        const unsigned b0 = bo0[seg * PW + i], b1 = bo1[seg * PW + i];
 #pragma unroll
         for (int ch = 0; ch < 2; ch++) {
           unsigned a0, a1, a2, a3;
           const unsigned la = st + o_lo[2 * i + ch], ha = st + o_hi[2 * i + ch];
           load_a(la, ha, a0, a2);
           load_a(la + 1024u, ha + 1024u, a1, a3);
-          const uint2 bb = ld64(ch == 0 ? bA_base + (unsigned)jg * bA_str : bB_base + (unsigned)(jg + 1) * bB_str);
-          mma_u8u8(c, a0, a1, a2, a3, bb.x, bb.y);
+          const unsigned m = ch == 0 ? maskA : maskB;
+          if constexpr (SIGNED_A) mma_s8u8(c, a0, a1, a2, a3, b0 & m, b1 & m);
+          else mma_u8u8(c, a0, a1, a2, a3, b0 & m, b1 & m);
         }
         // lane (sel, part): chunk jg+sel, digits 0-1 (part 0) or digit 2 and the ones column (part 1)
         const unsigned pa = st + g.off[2] + o_p[i];
         const float s0 = ldf(pa), s1 = ldf(pa + 1024u);
-        const float f = ldf(slot + MMA_SLOT_META + (unsigned)part * 4u);
+        float f;
+        if constexpr (FR_REGS) f = fr[seg * PW + i];
+        else f = ldf(slot + MMA_SLOT_META + (unsigned)part * 4u);   // dead pairs: the scale read from the tile is zero
         const float t0 = (float)(c[0] + c[1] * mulp), t1 = (float)(c[2] + c[3] * mulp);
         acc0 = fmaf(s0 * f, t0, acc0);
         acc1 = fmaf(s1 * f, t1, acc1);
@@ -379,7 +414,7 @@ gemv_mma_kernel(const WvDevBlob b, const float* __restrict__ xf, float* __restri
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar(fs));
-      MSTAMP(9 + 2 * (mt * g.nseg + seg));
+      MSTAMP(9 + 2 * (mt * NSEG + seg));
       if (++fs == g.nstage) { fs = 0; fpar ^= 1u; }
     }
     // 16 row sums of this block: over the quad, then over the warps
@@ -439,7 +474,7 @@ static bool mma_encode_plane(CUtensorMap* out, const void* base, unsigned rb, in
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int F, int PW>
+template <int F, int PW, int NSEG>
 static int launch_mma(const WvDevBlob& b, const float* dx, float* dy, int batch, int rb_, int re, cudaStream_t st) {
   constexpr WvFmtInfo fi = wv_fmt_info(F);
   MmaGeom g{};
@@ -447,6 +482,7 @@ static int launch_mma(const WvDevBlob& b, const float* dx, float* dy, int batch,
   g.cpr = b.cols >> 5;
   g.seg_chunks = 32 * PW;
   g.nseg = (g.cpr + g.seg_chunks - 1) / g.seg_chunks;
+  if (g.nseg != NSEG) return 1;
   if (g.cpr > MMA_WARPS * 32 || (g.cpr & 1)) return 1;   // one quantising thread per chunk; chunks are used in pairs
   const unsigned bpc[4] = {fi.bits_lo * 4u, fi.bits_hi * 4u, 4u, fi.has_min ? 4u : 0u};  // bytes per chunk (p0 / p1: per group)
   int ratio = 1;
@@ -509,7 +545,7 @@ static int launch_mma(const WvDevBlob& b, const float* dx, float* dy, int batch,
     maps = it->second;
   }
 
-  auto kern = gemv_mma_kernel<F, PW>;
+  auto kern = gemv_mma_kernel<F, PW, NSEG>;
   static unsigned attr_mask = 0;
   int dev = 0; cudaGetDevice(&dev);
   if (!(attr_mask & (1u << dev))) {
@@ -531,9 +567,23 @@ static int launch_mma(const WvDevBlob& b, const float* dx, float* dy, int batch,
 template <int F>
 static int launch_mma_format(const WvDevBlob& b, const float* dx, float* dy, int batch, int rb, int re, cudaStream_t st, int pw) {
   if constexpr (MmaCfg<F>::OK) {
-    if (pw == 1) return launch_mma<F, 1>(b, dx, dy, batch, rb, re, st);
-    if (pw == 4) { const int rc = launch_mma<F, 4>(b, dx, dy, batch, rb, re, st); if (rc != 1) return rc; }
-    return launch_mma<F, 2>(b, dx, dy, batch, rb, re, st);
+    // the segment count is a template parameter: per-pair operands live in registers
+    const int cpr = b.cols >> 5;
+    if (pw == 2) {
+      switch ((cpr + 63) / 64) {
+      case 1: return launch_mma<F, 2, 1>(b, dx, dy, batch, rb, re, st);
+      case 2: return launch_mma<F, 2, 2>(b, dx, dy, batch, rb, re, st);
+      case 4: return launch_mma<F, 2, 4>(b, dx, dy, batch, rb, re, st);
+      case 7: return launch_mma<F, 2, 7>(b, dx, dy, batch, rb, re, st);
+      }
+      return 1;
+    }
+    switch ((cpr + 127) / 128) {
+    case 1: return launch_mma<F, 4, 1>(b, dx, dy, batch, rb, re, st);
+    case 2: return launch_mma<F, 4, 2>(b, dx, dy, batch, rb, re, st);
+    case 3: return launch_mma<F, 4, 3>(b, dx, dy, batch, rb, re, st);
+    case 4: return launch_mma<F, 4, 4>(b, dx, dy, batch, rb, re, st);
+    }
   }
   return 1;
 }

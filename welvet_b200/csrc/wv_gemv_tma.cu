@@ -483,11 +483,12 @@ static int launch_tma_format(const WvDevBlob& b, const float* dx, float* dy, int
 }
 
 int wv_launch_gemv_tma(const WvDevBlob& b, const float* dx, float* dy, int batch, int row_begin, int row_end, cudaStream_t st) {
-  // tuning codes 21, 22, 24 send the formats with one parameter group per chunk to the tensor-pipe
-  // kernel (the digit is its chunk pairs per warp); it measures level with the dp4a kernel so far
-  // and is not the default
-  if (g_tma_rt >= 20) {
-    const int rc = wv_launch_gemv_mma(b, dx, dy, batch, row_begin, row_end, st, g_tma_rt - 20);
+  // Formats with one parameter group per chunk: rows of at most 4096 columns go to the tensor-pipe
+  // kernel (one column segment per 16-row block; measured 3-10 % faster there, level or slower on
+  // wider rows and for IQ3_XXS). Tuning codes 21, 22, 24 force it with that many chunk pairs per
+  // warp; any other non-zero code keeps everything on the dp4a kernel.
+  if (g_tma_rt >= 20 || (g_tma_rt == 0 && b.cols <= 4096 && b.format != WV_IQ3_XXS)) {
+    const int rc = wv_launch_gemv_mma(b, dx, dy, batch, row_begin, row_end, st, g_tma_rt >= 20 ? g_tma_rt - 20 : 4);
     if (rc != 1) return rc;
   }
   switch (b.format) {
