@@ -198,29 +198,45 @@ def main():
         del w
     torch.cuda.synchronize()
 
+    # N > 1: every rank owns a row range of every matrix and its kernels store their rows into
+    # all ranks' output vectors (peer mappings of one exportable buffer per rank): the gather is
+    # the GEMV's epilogue, there is no collective call inside the step and the step stays a graph.
+    gbufs = None
+    if world > 1:
+        from welvet_b200.dense import GatherBuffers
+
+        def exchange(h):
+            out = [None] * world
+            dist.all_gather_object(out, h)
+            return out
+        off = 0
+        for j in jobs:
+            j["off"] = off
+            off += j["rows"]
+        gbufs = GatherBuffers(4 * off, rank, world, exchange)
+        for j in jobs:
+            j["y_all"] = gbufs.pointers(j["off"])
+
     def launch(j, st):
-        _lib.check(L.wv_matvec_dev(j["key"], xs[j["cols"]].data_ptr(), j["y"].data_ptr() + j["r0"] * 4, 1, j["cols"], j["r1"] - j["r0"], st))
+        if world > 1:
+            _lib.check(L.wv_matvec_dev_gather(j["key"], xs[j["cols"]].data_ptr(), j["y_all"], world, rank, j["r0"], j["cols"], j["r1"] - j["r0"], st))
+        else:
+            _lib.check(L.wv_matvec_dev(j["key"], xs[j["cols"]].data_ptr(), j["y"].data_ptr(), 1, j["cols"], j["rows"], st))
 
     def step_plain():
         for j in jobs:
             launch(j, stream.cuda_stream)
-            if world > 1:
-                dist.all_gather_into_tensor(j["y"], j["y"][j["r0"]:j["r1"]])
 
     with torch.cuda.stream(stream):
         step_plain()                      # first call per kernel sets its attributes (not capturable)
     stream.synchronize()
-    graph = None
-    if world == 1:
-        # One CUDA graph per step: the 38 GEMV launches. With N > 1 the step is issued as plain
-        # launches: capturing the NCCL all-gathers in a graph made process-group teardown hang
-        # on this stack, and the sharded step is collective-latency bound either way.
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            cur = torch.cuda.current_stream().cuda_stream
-            for j in jobs:
-                launch(j, cur)
-    launch_mode = "cuda graph" if graph is not None else "plain"
+    # One CUDA graph per step: the 38 GEMV launches and nothing else, at every N.
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        cur = torch.cuda.current_stream().cuda_stream
+        for j in jobs:
+            launch(j, cur)
+    launch_mode = "cuda graph"
 
     def run_step():
         if graph is not None:
@@ -260,12 +276,32 @@ def main():
     value = full_bytes / (ms_step * 1e-3) / 1e9
     launches_per_step = len(jobs)   # 4096 / 14336 columns take the TMA-fed kernel: one launch per GEMV
 
+    gather_ok = None
     if world > 1:
-        # tear the process group down on every rank before any rank leaves: a graph that holds
-        # NCCL work and a peer that has already exited make destroy_process_group wait forever
-        graph = None
+        # the gathered vectors must equal the unsharded product's: checked on two jobs, on every rank
         torch.cuda.synchronize()
         dist.barrier()
+        ok = True
+        for j in (jobs[0], jobs[-1]):
+            w = torch.from_numpy(gen_weights(j["rows"], j["cols"])).cuda()
+            spec = next(f for f in sweep if f[0] == j["name"])
+            _lib.check(L.wv_pack_upload_dev(0x7FFF01, spec[1], spec[3], spec[2], w.data_ptr(), j["rows"], j["cols"], None))
+            ref = torch.zeros(j["rows"], device="cuda")
+            _lib.check(L.wv_matvec_dev(0x7FFF01, xs[j["cols"]].data_ptr(), ref.data_ptr(), 1, j["cols"], j["rows"], None))
+            torch.cuda.synchronize()
+            got = gbufs.read(j["off"], j["rows"])
+            ok = ok and bool(np.array_equal(got.view(np.uint32), ref.cpu().numpy().view(np.uint32)))
+            L.wv_blob_evict(0x7FFF01)
+            del w
+        t = torch.tensor([1.0 if ok else 0.0], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        gather_ok = bool(t.item() == 1.0)
+        # unmap the peers' buffers everywhere before any rank frees its own, then leave together
+        graph = None
+        gbufs.close_peers()
+        torch.cuda.synchronize()
+        dist.barrier()
+        gbufs.free_own()
         dist.destroy_process_group()
     if rank != 0:
         return
@@ -354,7 +390,9 @@ def main():
         "config": {"workload": "format_sweep_4096x14336+14336x4096", "formats": [f[0] for f in sweep], "batch": 1,
                    "weights": "N(0,0.02^2) seed 2", "activations": "N(0,1) seed 1",
                    "l2": "inputs larger than L2: one step streams %.0f MB of distinct packed weights" % (full_bytes / 1e6),
-                   "sharding": "rows split evenly across ranks, y all-gathered by NCCL" if world > 1 else "single GPU",
+                   "sharding": ("rows split evenly across ranks; each rank's GEMV kernels store their rows into every rank's y "
+                                "(peer mappings, no collective call); ranks synchronise around the timed region; gathered y verified: %s" % gather_ok)
+                   if world > 1 else "single GPU",
                    "launch": launch_mode,
                    "pct_of_8TBs": round(100 * value / NOMINAL_HBM_GBS, 1)},
         "gpu_launches": launches_per_step * args.steps,

@@ -110,6 +110,25 @@ int wv_pack_upload_dev(uint64_t key, int format, int dtype, int block_weights, c
  * share the array: calls that overlap on the GPU race — keep them on one stream. */
 int wv_matvec_dev_static(uint64_t key, const float* dx, float* dy, int in, int out, void* stream);
 
+/* Row-sharded GEMV whose epilogue is the gather: no counterpart call in the reference, where the
+ * goroutines of gemvPackedParallelF32 write disjoint row ranges of one y (layers/dense/gemv_parallel.go:24-41).
+ * Here every rank keeps rows [row_offset, row_offset + out_local) of the matrix resident (wv_blob_upload_shard) and
+ * the kernel stores each of its output rows into all `world` output vectors — its own and the peers' ones mapped
+ * into this process — so that every rank holds the whole y when all ranks' kernels have finished; there is no
+ * collective call and no extra launch on the bulk-copy kernels. y_all[r] is rank r's vector as addressable from
+ * this process (y_all[rank] is the local one); batch 1. The caller orders "all ranks finished" itself (a
+ * barrier between steps, or stream-ordered events), as it would around any collective. */
+int wv_matvec_dev_gather(uint64_t key, const float* dx, float* const* y_all, int world, int rank, int row_offset,
+                         int in, int out_local, void* stream);
+/* Plumbing for the vectors above (cudaMalloc + cudaIpcGetMemHandle / cudaIpcOpenMemHandle with lazy peer
+ * access): allocate an exportable device buffer and its 64-byte handle; map a peer's handle; unmap; free. */
+int wv_gather_alloc(size_t bytes, void** dptr, unsigned char handle[64]);
+int wv_gather_open(const unsigned char handle[64], void** dptr);
+int wv_gather_close(void* dptr);
+int wv_gather_free(void* dptr);
+/* Copy `bytes` from a gather buffer (own or mapped) to host memory after synchronising `stream`. */
+int wv_gather_read(const void* dptr, size_t offset_bytes, void* host, size_t bytes, void* stream);
+
 /* After the caller has synchronised its stream: 0, or WV_ETIMEOUT when a bounded device wait
  * of an asynchronous call (wv_matvec_dev) ran out since the last query. The reference reports
  * device failures through the error of the synchronous call (webgpu/affine_cache.go:439-443). */

@@ -3,6 +3,7 @@
 // resident caches (webgpu/affine_cache.go): one mutex around the key -> entry map, uploads
 // idempotent per key, dispatch outside the lock, hard errors and no host fallback.
 #include "wv_common.cuh"
+#include "wv_gemv_common.cuh"
 
 #include <cstdarg>
 #include <cstdio>
@@ -394,6 +395,76 @@ extern "C" int wv_matvec_dev(uint64_t key, const float* dx, float* dy, int batch
   rc = wv_launch_gemv(e.blob, dx, dy, batch, 0, e.blob.rows, static_cast<cudaStream_t>(stream));
   if (rc) wv_set_error("wv_matvec_dev: launch failed (%d): %s", rc, cudaGetErrorString(cudaGetLastError()));
   return rc;
+}
+
+extern "C" int wv_matvec_dev_gather(uint64_t key, const float* dx, float* const* y_all, int world, int rank, int row_offset,
+                                    int in, int out_local, void* stream) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!dx || !y_all) { wv_set_error("wv_matvec_dev_gather: null pointer"); return WV_EARG; }
+  if (world < 1 || world > WV_MAX_PEERS || rank < 0 || rank >= world || row_offset < 0) {
+    wv_set_error("wv_matvec_dev_gather: world=%d rank=%d row_offset=%d (at most %d ranks)", world, rank, row_offset, WV_MAX_PEERS);
+    return WV_EARG;
+  }
+  Entry e;
+  if ((rc = lookup(key, &e))) return rc;
+  if ((rc = check_dims(e, 1, in, out_local))) return rc;
+  WvPeers peers{};
+  peers.n = world; peers.self = rank;
+  for (int q = 0; q < world; q++) {
+    if (!y_all[q]) { wv_set_error("wv_matvec_dev_gather: y_all[%d] is null", q); return WV_EARG; }
+    peers.y[q] = y_all[q] + row_offset;
+  }
+  wv_cur_peers = &peers;
+  rc = wv_launch_gemv(e.blob, dx, peers.y[rank], 1, 0, e.blob.rows, static_cast<cudaStream_t>(stream));
+  wv_cur_peers = nullptr;
+  if (rc) wv_set_error("wv_matvec_dev_gather: launch failed (%d): %s", rc, cudaGetErrorString(cudaGetLastError()));
+  return rc;
+}
+
+extern "C" int wv_gather_alloc(size_t bytes, void** dptr, unsigned char handle[64]) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!dptr || !handle || !bytes) { wv_set_error("wv_gather_alloc: bad argument"); return WV_EARG; }
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  void* p = nullptr;
+  if (cudaMalloc(&p, bytes) != cudaSuccess) { cudaGetLastError(); wv_set_error("wv_gather_alloc: %zu bytes", bytes); return WV_ENOMEM; }
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) { cudaFree(p); wv_set_error("wv_gather_alloc: %s", cudaGetErrorString(e)); cudaGetLastError(); return WV_ECUDA; }
+  memcpy(handle, &h, 64);
+  CUDA_TRY(cudaMemset(p, 0, bytes));
+  *dptr = p;
+  return WV_OK;
+}
+extern "C" int wv_gather_open(const unsigned char handle[64], void** dptr) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!dptr || !handle) { wv_set_error("wv_gather_open: bad argument"); return WV_EARG; }
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  cudaError_t e = cudaIpcOpenMemHandle(dptr, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) { wv_set_error("wv_gather_open: %s", cudaGetErrorString(e)); cudaGetLastError(); return WV_ECUDA; }
+  return WV_OK;
+}
+extern "C" int wv_gather_close(void* dptr) {
+  if (!dptr) return WV_OK;
+  cudaError_t e = cudaIpcCloseMemHandle(dptr);
+  if (e != cudaSuccess) { wv_set_error("wv_gather_close: %s", cudaGetErrorString(e)); cudaGetLastError(); return WV_ECUDA; }
+  return WV_OK;
+}
+extern "C" int wv_gather_free(void* dptr) {
+  if (dptr && cudaFree(dptr) != cudaSuccess) { cudaGetLastError(); return WV_ECUDA; }
+  return WV_OK;
+}
+
+extern "C" int wv_gather_read(const void* dptr, size_t offset_bytes, void* host, size_t bytes, void* stream) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!dptr || !host) { wv_set_error("wv_gather_read: null pointer"); return WV_EARG; }
+  CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  CUDA_TRY(cudaMemcpy(host, static_cast<const unsigned char*>(dptr) + offset_bytes, bytes, cudaMemcpyDeviceToHost));
+  return WV_OK;
 }
 
 static int grow(float** p, size_t* cap, size_t n, bool pinned) {

@@ -515,13 +515,20 @@ static int launch_dense(const WvDevBlob& b, const float* dx, float* dy, int batc
   return WV_OK;
 }
 
-int wv_launch_gemv(const WvDevBlob& b, const float* dx, float* dy, int batch, int row_begin, int row_end, cudaStream_t st) {
-  if (row_end <= row_begin || batch <= 0) return WV_OK;
-  if (!b.fast) return wv_launch_gemv_ragged(b, dx, dy, batch, row_begin, row_end, st);
-  if (b.format != WV_NONE && !g_tune_r) {   // an explicit tuning override selects the register-load kernels
-    const int rc = wv_launch_gemv_tma(b, dx, dy, batch, row_begin, row_end, st);
-    if (rc != 1) return rc;
+thread_local const WvPeers* wv_cur_peers = nullptr;
+
+// Copies n floats of this GPU's slice to the same position of every other rank's vector (the
+// kernels without a peer-storing epilogue finish with this).
+__global__ void scatter_slice_kernel(const WvPeers peers, int n) {
+  const float* src = peers.y[peers.self];
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const float v = src[i];
+    for (int q = 0; q < peers.n; q++) if (q != peers.self) peers.y[q][i] = v;
   }
+}
+
+// Kernels that load planes through registers (and the FormatNone streaming kernel).
+static int launch_gemv_regs(const WvDevBlob& b, const float* dx, float* dy, int batch, int row_begin, int row_end, cudaStream_t st) {
   switch (b.format) {
   case WV_NONE:
     if (b.dtype == WV_DT_F32) return launch_dense<WV_DT_F32>(b, dx, dy, batch, row_begin, row_end, st);
@@ -535,6 +542,26 @@ int wv_launch_gemv(const WvDevBlob& b, const float* dx, float* dy, int batch, in
 #undef WV_F
   }
   return WV_EFORMAT;
+}
+
+int wv_launch_gemv(const WvDevBlob& b, const float* dx, float* dy, int batch, int row_begin, int row_end, cudaStream_t st) {
+  if (row_end <= row_begin || batch <= 0) return WV_OK;
+  const WvPeers* pp = wv_cur_peers;
+  if (pp && batch != 1) return WV_ESHAPE;
+  if (b.fast && b.format != WV_NONE && !g_tune_r) {   // an explicit tuning override selects the register-load kernels
+    const int rc = wv_launch_gemv_tma(b, dx, dy, batch, row_begin, row_end, st);   // stores to the peers in its epilogue
+    if (rc != 1) return rc;
+  }
+  // no peer-storing epilogue on the remaining paths: compute into the own vector, then copy the slice out
+  float* out = pp ? pp->y[pp->self] : dy;
+  const int rc = b.fast ? launch_gemv_regs(b, dx, out, batch, row_begin, row_end, st)
+                        : wv_launch_gemv_ragged(b, dx, out, batch, row_begin, row_end, st);
+  if (rc || !pp) return rc;
+  WvPeers shifted = *pp;
+  for (int q = 0; q < shifted.n; q++) shifted.y[q] += row_begin;
+  const int n = row_end - row_begin, blocks = (n + 255) / 256;
+  scatter_slice_kernel<<<blocks > 64 ? 64 : blocks, 256, 0, st>>>(shifted, n);
+  return cudaGetLastError() == cudaSuccess ? WV_OK : WV_ECUDA;
 }
 
 

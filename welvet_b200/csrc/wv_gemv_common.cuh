@@ -332,6 +332,18 @@ static cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
   return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
 
+// Output vectors of a row-sharded GEMV: with n > 0 every output row is stored into each of the n
+// vectors (this GPU's own and its peers' mapped ones) instead of into y, so that every rank ends
+// up with the whole result without a collective call.
+#define WV_MAX_PEERS 8
+struct WvPeers {
+  float* y[WV_MAX_PEERS];
+  int n;
+  int self;   // index of this GPU's own vector (host side only)
+};
+// Set by wv_matvec_dev_gather around its launch (wv_api.cu); the bulk-copy kernels pass it on.
+extern thread_local const WvPeers* wv_cur_peers;
+
 // wv_gemv.cu
 uint4* wv_scratch_take(size_t bytes);
 int wv_launch_xquant(int bits_lo, const float* dx, int cols, int batch, int imid, uint4* out, cudaStream_t st);

@@ -169,7 +169,7 @@ template <int F, int PW, int NSEG>
 __global__ void __launch_bounds__(MMA_THREADS, 1)
 gemv_mma_kernel(const WvDevBlob b, const float* __restrict__ xf, float* __restrict__ y, int row_begin, const MmaGeom g,
                 int* __restrict__ err, const __grid_constant__ CUtensorMap tm_lo, const __grid_constant__ CUtensorMap tm_hi,
-                const __grid_constant__ CUtensorMap tm_p0, const __grid_constant__ CUtensorMap tm_p1) {
+                const __grid_constant__ CUtensorMap tm_p0, const __grid_constant__ CUtensorMap tm_p1, const WvPeers peers) {
   constexpr WvFmtInfo fi = wv_fmt_info(F);
   constexpr int BL = fi.bits_lo, BH = fi.bits_hi;
   constexpr bool INT_MID = MmaCfg<F>::INT_MID, SIGNED_A = MmaCfg<F>::SIGNED_A;
@@ -429,7 +429,10 @@ gemv_mma_kernel(const WvDevBlob b, const float* __restrict__ xf, float* __restri
 #pragma unroll
       for (int q = 0; q < MMA_WARPS; q++) sum += base[q * 16];
       const int row = mt * 16 + lane;
-      if (row < band) yb[row] = sum;
+      if (row < band) {
+        if (peers.n == 0) yb[row] = sum;
+        else for (int q = 0; q < peers.n; q++) peers.y[q][row_begin + c_lo + row] = sum;   // own and peers' copies of y
+      }
     }
     par ^= 1;
     MSTAMP(36 + mt);
@@ -558,8 +561,10 @@ static int launch_mma(const WvDevBlob& b, const float* dx, float* dy, int batch,
   if (grid > total_mt) grid = total_mt;
   g.mt_base = total_mt / grid;
   g.mt_rem = total_mt % grid;
+  WvPeers peers{};
+  if (wv_cur_peers) { if (batch != 1) return WV_ESHAPE; peers = *wv_cur_peers; }
   cudaError_t e = launch_pdl(kern, dim3(grid, batch), dim3(MMA_THREADS), smem, st, b, dx, dy, rb_, g, wv_tma_err_ptr(),
-                             maps.m[0], maps.m[1], maps.m[2], maps.m[3]);
+                             maps.m[0], maps.m[1], maps.m[2], maps.m[3], peers);
   if (e != cudaSuccess) { wv_set_error("gemv (mma) launch: %s", cudaGetErrorString(e)); return WV_ECUDA; }
   return WV_OK;
 }

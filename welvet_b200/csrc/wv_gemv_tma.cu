@@ -111,7 +111,7 @@ __device__ __forceinline__ void load_frag_smem(FragT<F>& f, const LaneOff& a) {
 template <int F, int RT, bool PREFETCH>
 __global__ void __launch_bounds__(TMA_THREADS, 1)
 gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* __restrict__ xf, float* __restrict__ y,
-                int row_begin, int row_end, const TmaGeom g, int* __restrict__ err) {
+                int row_begin, int row_end, const TmaGeom g, int* __restrict__ err, const WvPeers peers) {
   constexpr WvFmtInfo fi = wv_fmt_info(F);
   constexpr int BL = fi.bits_lo;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -275,7 +275,10 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
       for (int q = 0; q < g.nwc; q++) sum += base[q * 32 + lane];
       const int n = batch_base + lane;
       const int row = c_lo + (n / RT) * g.tr + rg * RT + (n % RT);
-      if (n < nslots && (n / RT) * g.tr + rg * RT + (n % RT) < band && rg * RT + (n % RT) < g.tr) yb[row] = sum;
+      if (n < nslots && (n / RT) * g.tr + rg * RT + (n % RT) < band && rg * RT + (n % RT) < g.tr) {
+        if (peers.n == 0) yb[row] = sum;
+        else for (int q = 0; q < peers.n; q++) peers.y[q][row_begin + row] = sum;   // own and peers' copies of y
+      }
     }
     par ^= 1;
     keep = 0.f;
@@ -460,7 +463,9 @@ static int launch_tma(const WvDevBlob& b, const float* dx, float* dy, int batch,
   g.rows_base = nrows / grid;
   g.rows_rem = nrows % grid;
   const uint4* xq = nullptr;  // activations are quantised inside the kernel
-  cudaError_t e = launch_pdl(kern, dim3(grid, batch), dim3(TMA_THREADS), smem, st, b, xq, dx, dy, rb_, re, g, g_err_dev);
+  WvPeers peers{};
+  if (wv_cur_peers) { if (batch != 1) return WV_ESHAPE; peers = *wv_cur_peers; }
+  cudaError_t e = launch_pdl(kern, dim3(grid, batch), dim3(TMA_THREADS), smem, st, b, xq, dx, dy, rb_, re, g, g_err_dev, peers);
   if (e != cudaSuccess) { wv_set_error("gemv (tma) launch: %s", cudaGetErrorString(e)); return WV_ECUDA; }
   return WV_OK;
 }

@@ -111,3 +111,62 @@ def Forward(l: Optional[Layer], input: Optional[np.ndarray]) -> Tuple[np.ndarray
     if l.Exec.Backend == BackendCUDA:
         return ForwardCUDA(l, input)
     raise WelvetError(_lib.WV_EFORMAT, f"dense: backend {l.Exec.Backend} is not provided by welvet_b200 (CUDA only)")
+
+
+class GatherBuffers:
+    """Output vectors for row-sharded GEMVs whose epilogue is the gather (`wv_matvec_dev_gather`):
+    one exportable device buffer per rank, every rank's buffer mapped into every process. `exchange`
+    takes this rank's 64-byte handle and returns all ranks' handles in rank order (for example
+    `torch.distributed.all_gather_object`); with world == 1 it is not called."""
+
+    def __init__(self, nbytes: int, rank: int, world: int, exchange=None):
+        import ctypes as C
+        L = lib()
+        self.rank, self.world, self.nbytes = rank, world, nbytes
+        own = C.c_void_p()
+        handle = C.create_string_buffer(64)
+        check(L.wv_gather_alloc(nbytes, C.byref(own), handle))
+        self.own = own.value
+        self.ptrs = [None] * world
+        self.ptrs[rank] = self.own
+        if world > 1:
+            handles = exchange(handle.raw)
+            for r, h in enumerate(handles):
+                if r == rank:
+                    continue
+                p = C.c_void_p()
+                check(L.wv_gather_open(C.create_string_buffer(h, 64), C.byref(p)))
+                self.ptrs[r] = p.value
+        self._arr = (C.c_void_p * world)(*self.ptrs)
+
+    def pointers(self, offset_floats: int = 0):
+        """Array of `world` float pointers, each advanced by offset_floats (one y vector inside the buffers)."""
+        import ctypes as C
+        return (C.c_void_p * self.world)(*[p + 4 * offset_floats for p in self.ptrs])
+
+    def read(self, offset_floats: int, n: int, rank: Optional[int] = None, stream: int = 0) -> np.ndarray:
+        """n floats at offset_floats of rank's buffer (default: this rank's own) as a host array."""
+        out = np.empty(n, np.float32)
+        check(lib().wv_gather_read(self.ptrs[self.rank if rank is None else rank], 4 * offset_floats, out.ctypes.data, 4 * n, stream))
+        return out
+
+    def close_peers(self) -> None:
+        """Unmap the other ranks' buffers (every rank does this before any rank frees its own)."""
+        for r, p in enumerate(self.ptrs):
+            if p is not None and r != self.rank:
+                lib().wv_gather_close(p)
+                self.ptrs[r] = None
+
+    def free_own(self) -> None:
+        if self.ptrs[self.rank] is not None:
+            lib().wv_gather_free(self.ptrs[self.rank])
+            self.ptrs[self.rank] = None
+
+    def close(self) -> None:
+        self.close_peers()
+        self.free_own()
+
+
+def MatVecGatherCUDA(key: int, dx_ptr: int, y_all, world: int, rank: int, row_offset: int, in_: int, out_local: int, stream: int = 0) -> None:
+    """Row-sharded y = W x whose kernel stores this rank's rows into every rank's y (no collective)."""
+    check(lib().wv_matvec_dev_gather(key, dx_ptr, y_all, world, rank, row_offset, in_, out_local, stream))
