@@ -146,6 +146,8 @@ def run_reference(args, rank, world):
 
 # ------------------------------------------------------------------------------ product arm
 def main():
+    # NCCL prints its version line to stdout when NCCL_DEBUG asks for it; stdout carries the one JSON line
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)

@@ -104,3 +104,41 @@ def test_decoder_block_single_token_decode(wv):
         assert np.all(err <= TOL * den + 1e-30), name
     # and the block output agrees end to end
     assert np.max(np.abs(y_dev - y_ref)) <= 2e-3 * np.max(np.abs(y_ref))
+
+
+@pytest.mark.parametrize("fmt", ["Q8_0", "Q4_K"])
+def test_lm_head_shape(wv, fmt):
+    """The largest single matrix of the configurations: an LM head of 128256 x 8192 (1.05 G weights,
+    1.18 GB in Q8_0). Packed on the device, multiplied on the device, checked against the restated
+    SIMD path on every row; the same blob split into 8 row shards must reassemble to the same y."""
+    import ctypes as C
+    rows, cols = 128256, 8192
+    rng = np.random.default_rng(5)
+    w = rng.standard_normal(rows * cols, dtype=np.float32)
+    w *= np.float32(0.02)
+    x = rng.standard_normal(cols, dtype=np.float32)
+    blob = wv.quant.Pack(wv.quant.Format(O.FMT[fmt]), w, rows, cols)
+    del w
+    y = np.zeros(rows, np.float32)
+    wv.dense.MatVecPackedBlob(blob, x, y)
+    ob = O.Blob(O.FMT[fmt], rows, cols, blob.Raw, blob.Scales, blob.Mins, blob.BlockWeights)
+    ref = O.matvec_simd(ob, x, 0)
+    den = O.sum_abs_wx(ob, x)
+    err = np.abs(y.astype(np.float64) - ref.astype(np.float64))
+    assert np.all(err <= TOL * den + 1e-30), float(np.max(err / np.maximum(den, 1e-30)))
+    # 8 row shards (16032 rows each), each computed on its own, give back the same vector
+    L = wv._lib.lib()
+    import torch
+    dx = torch.from_numpy(x).cuda()
+    dy = torch.zeros(rows, device="cuda")
+    world = 8
+    for r in range(world):
+        key = 0xB20000 + r
+        wv._lib.check(L.wv_blob_upload_shard(key, O.FMT[fmt], 1, rows, cols, blob.BlockWeights, blob.Raw.ctypes.data, blob.Raw.size,
+                                             None, 0, None, 0, r, world))
+        r0, r1 = C.c_int(), C.c_int()
+        wv._lib.check(L.wv_shard_range(rows, r, world, C.byref(r0), C.byref(r1)))
+        wv._lib.check(L.wv_matvec_dev(key, dx.data_ptr(), dy.data_ptr() + 4 * r0.value, 1, cols, r1.value - r0.value, None))
+        torch.cuda.synchronize()
+        L.wv_blob_evict(key)
+    assert np.array_equal(dy.cpu().numpy().view(np.uint32), y.view(np.uint32))

@@ -44,8 +44,8 @@ static std::unordered_map<uint64_t, Entry> g_cache;
 static uint64_t g_cache_bytes = 0, g_cache_limit = 0;
 static int g_device = -1;
 static cudaStream_t g_stream = nullptr;
-static float *g_hx = nullptr, *g_hy = nullptr, *g_dx = nullptr, *g_dy = nullptr;
-static size_t g_hx_n = 0, g_hy_n = 0, g_dx_n = 0, g_dy_n = 0;
+static float *g_hx = nullptr, *g_hy = nullptr, *g_dx = nullptr, *g_hy_dev = nullptr;
+static size_t g_hx_n = 0, g_hy_n = 0, g_dx_n = 0;
 
 extern "C" int wv_device_count(void) {
   int n = 0;
@@ -486,13 +486,20 @@ extern "C" int wv_matvec(uint64_t key, const float* x, float* y, int batch, int 
   if ((rc = check_dims(e, batch, in, out))) return rc;
   const size_t nx = (size_t)batch * in, ny = (size_t)batch * out;
   std::lock_guard<std::mutex> lk(g_stage_mu);
-  if ((rc = grow(&g_hx, &g_hx_n, nx, true)) || (rc = grow(&g_hy, &g_hy_n, ny, true)) ||
-      (rc = grow(&g_dx, &g_dx_n, nx, false)) || (rc = grow(&g_dy, &g_dy_n, ny, false))) return rc;
+  if ((rc = grow(&g_hx, &g_hx_n, nx, true)) || (rc = grow(&g_dx, &g_dx_n, nx, false))) return rc;
+  // y lives in mapped pinned host memory: the kernels write each output once with plain stores, so
+  // they store straight to the host and the call needs no device-to-host copy
+  if (g_hy_n < ny) {
+    if (g_hy) { cudaFreeHost(g_hy); g_hy = nullptr; g_hy_n = 0; }
+    const size_t want = ny + ny / 2 + 1024;
+    if (cudaHostAlloc(&g_hy, want * 4, cudaHostAllocMapped) != cudaSuccess) { cudaGetLastError(); wv_set_error("staging allocation of %zu floats failed", want); return WV_ENOMEM; }
+    if (cudaHostGetDevicePointer(&g_hy_dev, g_hy, 0) != cudaSuccess) { cudaGetLastError(); cudaFreeHost(g_hy); g_hy = nullptr; wv_set_error("no device alias for the output staging buffer"); return WV_ECUDA; }
+    g_hy_n = want;
+  }
   memcpy(g_hx, x, nx * 4);
   CUDA_TRY(cudaMemcpyAsync(g_dx, g_hx, nx * 4, cudaMemcpyHostToDevice, g_stream));
-  rc = wv_launch_gemv(e.blob, g_dx, g_dy, batch, 0, e.blob.rows, g_stream);
+  rc = wv_launch_gemv(e.blob, g_dx, g_hy_dev, batch, 0, e.blob.rows, g_stream);
   if (rc) { wv_set_error("wv_matvec: launch failed (%d): %s", rc, cudaGetErrorString(cudaGetLastError())); return rc; }
-  CUDA_TRY(cudaMemcpyAsync(g_hy, g_dy, ny * 4, cudaMemcpyDeviceToHost, g_stream));
   CUDA_TRY(cudaStreamSynchronize(g_stream));
   if (int te = wv_tma_take_error()) { wv_set_error("wv_matvec: a bounded device wait ran out (code %d)", te); return WV_ETIMEOUT; }
   memcpy(y, g_hy, ny * 4);
