@@ -83,6 +83,14 @@ int wv_matvec(uint64_t key, const float* x, float* y, int batch, int in, int out
  * chained decode and for benchmarking with inputs resident in HBM. */
 int wv_matvec_dev(uint64_t key, const float* dx, float* dy, int batch, int in, int out, void* stream);
 
+/* Several matrices that share x in one launch — the reference's fused projection groups: Q|K|V
+ * (fusedgpu/shaders.go:59-157; on the host mha/cpu.go:48-96 runs three dense forwards on one input) and SwiGLU gate|up
+ * (fusedgpu/shaders.go:159-222, swiglu/cpu.go:29-52). y_i[batch, out_i] = x[batch, in] . W_i^T for i < n, n <= 4.
+ * Matrices of one format, column count and group run as ONE kernel that waits for its predecessor, brings x in and
+ * quantises it once; any other mix runs as n launches with the same results. Device pointers, asynchronous. */
+int wv_matvec_dev_multi(const uint64_t* keys, int n, const float* dx, float* const* dy, int batch, int in, const int* out,
+                        void* stream);
+
 /* Dequantise the resident blob to f32 on the device and copy rows*cols floats out —
  * quant.Unpack (quant/unpack.go:4-34); results are bit-identical to it. */
 int wv_unpack(uint64_t key, float* out_host);

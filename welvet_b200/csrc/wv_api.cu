@@ -397,6 +397,34 @@ extern "C" int wv_matvec_dev(uint64_t key, const float* dx, float* dy, int batch
   return rc;
 }
 
+extern "C" int wv_matvec_dev_multi(const uint64_t* keys, int n, const float* dx, float* const* dy, int batch, int in, const int* out,
+                                   void* stream) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!keys || !dx || !dy || !out || n < 1 || n > 4) { wv_set_error("wv_matvec_dev_multi: bad argument (1..4 matrices)"); return WV_EARG; }
+  WvDevBlob blobs[4];
+  for (int i = 0; i < n; i++) {
+    if (!dy[i]) { wv_set_error("wv_matvec_dev_multi: dy[%d] is null", i); return WV_EARG; }
+    Entry e;
+    if ((rc = lookup(keys[i], &e))) return rc;
+    if ((rc = check_dims(e, batch, in, out[i]))) return rc;
+    blobs[i] = e.blob;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (n > 1 && blobs[0].fast && blobs[0].format != WV_NONE) {
+    rc = wv_launch_gemv_tma_group(blobs, n, dx, dy, batch, 0, 0, st);
+    if (rc != 1) {
+      if (rc) wv_set_error("wv_matvec_dev_multi: launch failed (%d): %s", rc, cudaGetErrorString(cudaGetLastError()));
+      return rc;
+    }
+  }
+  for (int i = 0; i < n; i++) {
+    rc = wv_launch_gemv(blobs[i], dx, dy[i], batch, 0, blobs[i].rows, st);
+    if (rc) { wv_set_error("wv_matvec_dev_multi: launch %d failed (%d): %s", i, rc, cudaGetErrorString(cudaGetLastError())); return rc; }
+  }
+  return WV_OK;
+}
+
 extern "C" int wv_matvec_dev_gather(uint64_t key, const float* dx, float* const* y_all, int world, int rank, int row_offset,
                                     int in, int out_local, void* stream) {
   int rc = ensure_init();

@@ -35,11 +35,21 @@ struct TmaGeom {
   unsigned stage_bytes;
   unsigned off[5];   // lo, hi, p0, p1, km section offsets inside a stage
   unsigned rb[5];    // bytes per row of each plane (0 = plane absent)
-  int rows_base, rows_rem;  // CTA b owns rows_base (+1 if b < rows_rem) consecutive rows
   int lead;          // tiles issued before the producer waits for the activation loads to be on their way
   unsigned x_off;    // staged activations: 33 floats per chunk (32 + one of padding)
   unsigned red_off;  // float red[2][nrg][nwc][32]
   unsigned bar_off;  // full[nstage], empty[nstage]
+};
+
+// The matrices one launch works through (same format, columns and group; they share x): the
+// planes, output vector and row split of each. A plain GEMV is a group of one.
+#define TMA_MAX_GROUP 4
+struct TmaGroup {
+  int n;
+  int rows[TMA_MAX_GROUP];
+  int rows_base[TMA_MAX_GROUP], rows_rem[TMA_MAX_GROUP];   // CTA b owns rows_base (+1 if b < rows_rem) consecutive rows of matrix i
+  const void* plane[TMA_MAX_GROUP][5];                      // lo, hi, p0, p1, km
+  float* y[TMA_MAX_GROUP];
 };
 
 // Sticky code of the first bounded wait that ran out, in mapped pinned host memory so that the
@@ -110,7 +120,7 @@ __device__ __forceinline__ void load_frag_smem(FragT<F>& f, const LaneOff& a) {
 
 template <int F, int RT, bool PREFETCH>
 __global__ void __launch_bounds__(TMA_THREADS, 1)
-gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* __restrict__ xf, float* __restrict__ y,
+gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* __restrict__ xf, const TmaGroup grp,
                 int row_begin, int row_end, const TmaGeom g, int* __restrict__ err, const WvPeers peers) {
   constexpr WvFmtInfo fi = wv_fmt_info(F);
   constexpr int BL = fi.bits_lo;
@@ -118,12 +128,16 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   __shared__ int s_abort;
   __shared__ unsigned s_xissued;   // consumer warps that have issued their loads of x
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  // band of this CTA without divisions: the host splits the rows as evenly as possible
+  // band of this CTA in matrix i, without divisions: the host splits the rows as evenly as possible
   const int bid = blockIdx.x;
-  const int band = g.rows_base + (bid < g.rows_rem ? 1 : 0);
-  const int c_lo = bid * g.rows_base + min(bid, g.rows_rem), c_hi = c_lo + band;
-  const int ntiles = (band + g.tr - 1) / g.tr;
-  (void)row_end;
+  int band, c_lo, c_hi, ntiles;
+  auto set_band = [&](int i) {
+    band = grp.rows_base[i] + (bid < grp.rows_rem[i] ? 1 : 0);
+    c_lo = bid * grp.rows_base[i] + min(bid, grp.rows_rem[i]);
+    c_hi = c_lo + band;
+    ntiles = (band + g.tr - 1) / g.tr;
+  };
+  (void)row_end; (void)xqg;
   const unsigned bar0 = smem_u32(smem + g.bar_off);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (g.nstage + s); };
@@ -144,12 +158,12 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   if (warp == TMA_CONSUMER_WARPS) {
     // ------------------------------------------------------------ producer
     // One thread issues the copies; the other lanes of the warp have nothing to do.
-    const void* src[5] = {b.lo, b.hi, b.p0, b.p1, b.km};
     bool dead = false;
-    int issued = 0;
+    int issued = 0;        // tiles issued so far, over all matrices
     int ps = 0;            // stage of the tile being issued
     unsigned ppar = 1;     // parity of the "empty" phase to wait for once the ring has wrapped
     bool wrapped = false;
+    int bi = 0;            // matrix being streamed
     auto issue_tile = [&](int t) {
       const int s = ps;
       if (wrapped) {
@@ -168,22 +182,29 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
       const unsigned dst = smem_u32(smem) + (unsigned)s * g.stage_bytes;
 #pragma unroll
       for (int i = 0; i < 5; i++) {
-        if (g.rb[i]) bulk_g2s(dst + g.off[i], (const unsigned char*)src[i] + (size_t)(row_begin + r0) * g.rb[i], g.rb[i] * nr, full_bar(s));
+        if (g.rb[i]) bulk_g2s(dst + g.off[i], (const unsigned char*)grp.plane[bi][i] + (size_t)(row_begin + r0) * g.rb[i], g.rb[i] * nr, full_bar(s));
       }
-      issued = t + 1;
-      WV_STAMP_ANY(40 + t);
+      WV_STAMP_ANY(40 + issued);
+      issued++;
       if (++ps == g.nstage) { ps = 0; wrapped = true; ppar ^= 1u; }
     };
     if (lane == 0) {
-      int t = 0;
-      for (; t < ntiles && t < g.lead && !dead; t++) issue_tile(t);
-      // The activation loads must not queue behind a full ring of weight traffic: after the
-      // first tiles, hold further copies until every consumer warp has issued its loads of x
-      // (a relaxed counter: a barrier here would wait for the loads to complete).
-      for (unsigned i = 0; i < TMA_SPIN_LIMIT; i++) {
-        if (*(volatile unsigned*)&s_xissued >= TMA_CONSUMER_WARPS) break;
+      bool held = false;
+      for (bi = 0; bi < grp.n && !dead; bi++) {
+        set_band(bi);
+        for (int t = 0; t < ntiles && !dead; t++) {
+          if (!held && issued >= g.lead) {
+            // The activation loads must not queue behind a full ring of weight traffic: after the
+            // first tiles, hold further copies until every consumer warp has issued its loads of x
+            // (a relaxed counter: a barrier here would wait for the loads to complete).
+            held = true;
+            for (unsigned i = 0; i < TMA_SPIN_LIMIT; i++) {
+              if (*(volatile unsigned*)&s_xissued >= TMA_CONSUMER_WARPS) break;
+            }
+          }
+          issue_tile(t);
+        }
       }
-      for (; t < ntiles && !dead; t++) issue_tile(t);
       // drain: every copy issued must have landed before the CTA gives its shared memory back
       for (int t = max(0, issued - g.nstage); t < issued; t++) {
         if (!mbar_wait(full_bar(t % g.nstage), (t / g.nstage) & 1)) { atomicCAS_system(err, 0, 200 + t % g.nstage); break; }
@@ -260,11 +281,11 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   }
   WV_STAMP(2);
   float* red = reinterpret_cast<float*>(smem + g.red_off);
-  float* yb = y + (size_t)blockIdx.y * b.rows + row_begin;
+  float* yb = nullptr;
   float keep = 0.f;
   int par = 0;
   bool dead = false;
-  const int nslots = ntiles * RT;
+  int nslots = 0;
   auto flush = [&](int batch_base) {
     float* mine = red + (((size_t)par * g.nrg + rg) * g.nwc + wc) * 32;
     mine[lane] = keep;
@@ -318,6 +339,10 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
     if (++fs == g.nstage) { fs = 0; fpar ^= 1u; }
   };
 
+  for (int bi = 0; bi < grp.n; bi++) {   // one matrix after the other; ring position and x registers carry over
+  set_band(bi);
+  nslots = ntiles * RT;
+  yb = grp.y[bi] + (size_t)blockIdx.y * grp.rows[bi] + row_begin;
   FragT<F> nxt[PREFETCH ? RT : 1];
   if constexpr (PREFETCH) { if (ntiles > 0) { wait_tile(true); fetch_tile(nxt); } }
   WV_STAMP(3);
@@ -393,6 +418,7 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
     if constexpr (PREFETCH) { if (!fetched) { wait_tile(true); fetch_tile(nxt); } }
   }
   if (nslots & 31) flush(nslots & ~31);
+  }
   WV_STAMP(4);
   WV_STAMP_NS(7);
 }
@@ -423,8 +449,9 @@ extern "C" void wv_set_tma_tuning(int rows_per_group, int stages) { g_tma_rt = r
 int wv_tma_tuning_stages() { return g_tma_stages; }
 
 template <int F, int RT, bool PF>
-static int launch_tma(const WvDevBlob& b, const float* dx, float* dy, int batch, int rb_, int re, cudaStream_t st) {
+static int launch_tma(const WvDevBlob* bl, int nb, const float* dx, float* const* dys, int batch, int rb_, int re, cudaStream_t st) {
   constexpr WvFmtInfo fi = wv_fmt_info(F);
+  const WvDevBlob& b = bl[0];   // the matrices of a group agree in everything but their row count
   TmaGeom g{};
   if (!plane_row_bytes(b, g.rb)) return 1;
   g.cpr = b.cols >> 5;
@@ -458,33 +485,40 @@ static int launch_tma(const WvDevBlob& b, const float* dx, float* dy, int batch,
     attr_mask |= 1u << dev;
   }
   int grid = wv_sm_count();
-  const int nrows = re - rb_;
-  if (grid > nrows) grid = nrows;
-  g.rows_base = nrows / grid;
-  g.rows_rem = nrows % grid;
+  TmaGroup grp{};
+  grp.n = nb;
+  if (nb == 1 && grid > re - rb_) grid = re - rb_;
+  for (int i = 0; i < nb; i++) {
+    const int nrows = nb == 1 ? re - rb_ : bl[i].rows;
+    grp.rows[i] = bl[i].rows;
+    grp.rows_base[i] = nrows / grid;
+    grp.rows_rem[i] = nrows % grid;
+    grp.plane[i][0] = bl[i].lo; grp.plane[i][1] = bl[i].hi; grp.plane[i][2] = bl[i].p0; grp.plane[i][3] = bl[i].p1; grp.plane[i][4] = bl[i].km;
+    grp.y[i] = dys[i];
+  }
   const uint4* xq = nullptr;  // activations are quantised inside the kernel
   WvPeers peers{};
-  if (wv_cur_peers) { if (batch != 1) return WV_ESHAPE; peers = *wv_cur_peers; }
-  cudaError_t e = launch_pdl(kern, dim3(grid, batch), dim3(TMA_THREADS), smem, st, b, xq, dx, dy, rb_, re, g, g_err_dev, peers);
+  if (wv_cur_peers) { if (batch != 1 || nb != 1) return WV_ESHAPE; peers = *wv_cur_peers; }
+  cudaError_t e = launch_pdl(kern, dim3(grid, batch), dim3(TMA_THREADS), smem, st, b, xq, dx, grp, rb_, re, g, g_err_dev, peers);
   if (e != cudaSuccess) { wv_set_error("gemv (tma) launch: %s", cudaGetErrorString(e)); return WV_ECUDA; }
   return WV_OK;
 }
 
 template <int F>
-static int launch_tma_format(const WvDevBlob& b, const float* dx, float* dy, int batch, int rb, int re, cudaStream_t st) {
+static int launch_tma_format(const WvDevBlob* b, int nb, const float* dx, float* const* dy, int batch, int rb, int re, cudaStream_t st) {
   constexpr WvFmtInfo fi = wv_fmt_info(F);
   // tuning codes: 1, 2, 4 = rows per group with register prefetch of the next tile; 11, 12, 14, 8 = without
   // measured best everywhere: four rows per group, fragments fetched right before use (a second
   // fragment set in registers costs more in register pressure than it hides in latency)
   int rt = (g_tma_rt && g_tma_rt < 20) ? g_tma_rt : 14;
   switch (rt) {
-  case 1: return launch_tma<F, 1, true>(b, dx, dy, batch, rb, re, st);
-  case 2: return launch_tma<F, 2, true>(b, dx, dy, batch, rb, re, st);
-  case 12: return launch_tma<F, 2, false>(b, dx, dy, batch, rb, re, st);
-  case 8: if constexpr (fi.bits_lo < 8) return launch_tma<F, 8, false>(b, dx, dy, batch, rb, re, st); break;
+  case 1: return launch_tma<F, 1, true>(b, nb, dx, dy, batch, rb, re, st);
+  case 2: return launch_tma<F, 2, true>(b, nb, dx, dy, batch, rb, re, st);
+  case 12: return launch_tma<F, 2, false>(b, nb, dx, dy, batch, rb, re, st);
+  case 8: if constexpr (fi.bits_lo < 8) return launch_tma<F, 8, false>(b, nb, dx, dy, batch, rb, re, st); break;
   }
-  if (rt == 4) return launch_tma<F, 4, true>(b, dx, dy, batch, rb, re, st);
-  return launch_tma<F, 4, false>(b, dx, dy, batch, rb, re, st);
+  if (rt == 4) return launch_tma<F, 4, true>(b, nb, dx, dy, batch, rb, re, st);
+  return launch_tma<F, 4, false>(b, nb, dx, dy, batch, rb, re, st);
 }
 
 int wv_launch_gemv_tma(const WvDevBlob& b, const float* dx, float* dy, int batch, int row_begin, int row_end, cudaStream_t st) {
@@ -496,8 +530,20 @@ int wv_launch_gemv_tma(const WvDevBlob& b, const float* dx, float* dy, int batch
     const int rc = wv_launch_gemv_mma(b, dx, dy, batch, row_begin, row_end, st, g_tma_rt >= 20 ? g_tma_rt - 20 : 4);
     if (rc != 1) return rc;
   }
-  switch (b.format) {
-#define WV_F(f) case f: return launch_tma_format<f>(b, dx, dy, batch, row_begin, row_end, st);
+  float* dys[1] = {dy};
+  return wv_launch_gemv_tma_group(&b, 1, dx, dys, batch, row_begin, row_end, st);
+}
+
+// Several matrices of one format, column count and group that share x (Q|K|V, gate|up) in one
+// launch: the prologue (wait for the preceding kernel, bring x in, quantise it) is paid once.
+// Returns 1 when the group cannot run as one launch of this kernel.
+int wv_launch_gemv_tma_group(const WvDevBlob* b, int nb, const float* dx, float* const* dy, int batch, int row_begin, int row_end,
+                             cudaStream_t st) {
+  if (nb < 1 || nb > TMA_MAX_GROUP) return 1;
+  for (int i = 1; i < nb; i++)
+    if (b[i].format != b[0].format || b[i].cols != b[0].cols || b[i].group != b[0].group || b[i].dtype != b[0].dtype || !b[i].fast) return 1;
+  switch (b[0].format) {
+#define WV_F(f) case f: return launch_tma_format<f>(b, nb, dx, dy, batch, row_begin, row_end, st);
   WV_F(WV_Q8_0) WV_F(WV_Q4_0) WV_F(WV_Q4_1) WV_F(WV_Q5_0) WV_F(WV_Q5_1)
   WV_F(WV_Q2_K) WV_F(WV_Q3_K) WV_F(WV_Q4_K) WV_F(WV_Q5_K) WV_F(WV_Q6_K)
   WV_F(WV_IQ1_S) WV_F(WV_IQ2_XXS) WV_F(WV_IQ2_XS) WV_F(WV_IQ3_XXS) WV_F(WV_IQ3_S) WV_F(WV_IQ4_NL) WV_F(WV_IQ4_XS)

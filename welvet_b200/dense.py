@@ -170,3 +170,15 @@ class GatherBuffers:
 def MatVecGatherCUDA(key: int, dx_ptr: int, y_all, world: int, rank: int, row_offset: int, in_: int, out_local: int, stream: int = 0) -> None:
     """Row-sharded y = W x whose kernel stores this rank's rows into every rank's y (no collective)."""
     check(lib().wv_matvec_dev_gather(key, dx_ptr, y_all, world, rank, row_offset, in_, out_local, stream))
+
+
+def MatVecGroupCUDA(stores, dx_ptr: int, dy_ptrs, batch: int, in_: int, stream: int = 0) -> None:
+    """Projection group (Q|K|V, gate|up): y_i = x W_i^T for every store of the list on one shared x, as one
+    launch when the stores agree in format and columns (the reference's fused shaders, fusedgpu/shaders.go:59-222).
+    Device pointers: dx_ptr to x[batch, in], dy_ptrs[i] to y_i[batch, out_i]."""
+    import ctypes as C
+    n = len(stores)
+    keys = (C.c_uint64 * n)(*[quant.EnsureResident(s.Packed) for s in stores])
+    outs = (C.c_int * n)(*[s.Rows for s in stores])
+    dys = (C.c_void_p * n)(*dy_ptrs)
+    check(lib().wv_matvec_dev_multi(keys, n, dx_ptr, dys, batch, in_, outs, stream))
