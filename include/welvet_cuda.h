@@ -91,6 +91,13 @@ int wv_matvec_dev(uint64_t key, const float* dx, float* dy, int batch, int in, i
 int wv_matvec_dev_multi(const uint64_t* keys, int n, const float* dx, float* const* dy, int batch, int in, const int* out,
                         void* stream);
 
+/* Greedy pick on the device — sampling.ArgMax (model/sampling/argmax.go:4-18; the reference's fused path does the same
+ * in a shader, fusedgpu/shaders.go:471-510): index of the first strict maximum of n device floats, so that the
+ * 128256 logits of an LM head need not be read back. wv_argmax_dev writes the index to device memory on `stream`;
+ * wv_argmax synchronises and returns it to the host. */
+int wv_argmax_dev(const float* d_logits, int n, int* d_index, void* stream);
+int wv_argmax(const float* d_logits, int n, int* index_host, void* stream);
+
 /* Dequantise the resident blob to f32 on the device and copy rows*cols floats out —
  * quant.Unpack (quant/unpack.go:4-34); results are bit-identical to it. */
 int wv_unpack(uint64_t key, float* out_host);

@@ -212,3 +212,9 @@ def wire_decode(fmt, rows, cols, wire: np.ndarray, dtype: int = DT_F32) -> Blob:
     mins = wire[om:om + 4 * nm].copy().view(np.float32)
     raw = wire[orr:orr + nr].copy()
     return Blob(f, rows, cols, raw, scales, mins, bw.value, dtype)
+
+
+def argmax(logits: np.ndarray) -> int:
+    """sampling.ArgMax (model/sampling/argmax.go:4-18)."""
+    v = np.ascontiguousarray(logits, np.float32).reshape(-1)
+    return int(lib().wvo_argmax(v.ctypes.data_as(C.c_void_p), C.c_int64(v.size)))

@@ -1279,3 +1279,17 @@ int wvo_wire_decode(int format, int rows, int cols, const uint8_t *wire, uint64_
   }
   return 0;
 }
+
+/* ---------- greedy sampling (model/sampling/argmax.go:4-18) ----------
+ * First index of the strict maximum: `v > maxVal` never holds for NaN, so NaN never wins, and a
+ * NaN in position 0 keeps index 0. Empty input returns 0. */
+int wvo_argmax(const float *logits, int64_t n) {
+  if (n <= 0) return 0;
+  int64_t max_idx = 0;
+  float max_val = logits[0];
+  for (int64_t i = 0; i < n; i++) {
+    float v = logits[i];
+    if (v > max_val) { max_val = v; max_idx = i; }
+  }
+  return (int)max_idx;
+}

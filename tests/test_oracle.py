@@ -161,3 +161,14 @@ def test_golden_fixtures():
             assert np.array_equal(b.scales, g[k + "_scales"]) and np.array_equal(b.mins, g[k + "_mins"]), k
             assert np.array_equal(O.unpack(b).view(np.uint32), g[k + "_unpack"].view(np.uint32)), k
             assert np.array_equal(O.matvec(b, x), g[k + "_y_scalar"]), k
+
+
+def test_argmax_restatement():
+    """sampling.ArgMax: first strict maximum; NaN never wins; NaN in position 0 keeps index 0; empty -> 0."""
+    assert O.argmax(np.array([1, 3, 3, 2], np.float32)) == 1
+    assert O.argmax(np.array([np.nan, 3, 3, 2], np.float32)) == 0
+    assert O.argmax(np.array([1, np.nan, 0.5], np.float32)) == 0
+    assert O.argmax(np.array([-np.inf, -np.inf], np.float32)) == 0
+    assert O.argmax(np.zeros(0, np.float32)) == 0
+    v = np.random.default_rng(0).normal(0, 1, 5000).astype(np.float32)
+    assert O.argmax(v) == int(np.argmax(v))

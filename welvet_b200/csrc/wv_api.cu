@@ -397,6 +397,34 @@ extern "C" int wv_matvec_dev(uint64_t key, const float* dx, float* dy, int batch
   return rc;
 }
 
+int wv_launch_argmax(const float* d_logits, int n, int* d_out, cudaStream_t st);   // wv_gemv.cu
+
+extern "C" int wv_argmax_dev(const float* d_logits, int n, int* d_index, void* stream) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!d_logits || !d_index || n < 0) { wv_set_error("wv_argmax_dev: bad argument"); return WV_EARG; }
+  return wv_launch_argmax(d_logits, n, d_index, static_cast<cudaStream_t>(stream));
+}
+extern "C" int wv_argmax(const float* d_logits, int n, int* index_host, void* stream) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!d_logits || !index_host || n < 0) { wv_set_error("wv_argmax: bad argument"); return WV_EARG; }
+  static int* h_idx = nullptr;     // mapped pinned word: the kernel writes the index straight to the host
+  static int* d_idx = nullptr;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lk(mu);
+  if (!h_idx) {
+    if (cudaHostAlloc(&h_idx, sizeof(int), cudaHostAllocMapped) != cudaSuccess || cudaHostGetDevicePointer(&d_idx, h_idx, 0) != cudaSuccess) {
+      cudaGetLastError(); h_idx = nullptr; wv_set_error("wv_argmax: no pinned word"); return WV_ENOMEM;
+    }
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if ((rc = wv_launch_argmax(d_logits, n, d_idx, st))) return rc;
+  CUDA_TRY(cudaStreamSynchronize(st));
+  *index_host = *h_idx;
+  return WV_OK;
+}
+
 extern "C" int wv_matvec_dev_multi(const uint64_t* keys, int n, const float* dx, float* const* dy, int batch, int in, const int* out,
                                    void* stream) {
   int rc = ensure_init();

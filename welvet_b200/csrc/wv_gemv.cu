@@ -515,6 +515,47 @@ static int launch_dense(const WvDevBlob& b, const float* dx, float* dy, int batc
   return WV_OK;
 }
 
+// ------------------------------------------------------------------ greedy pick over the logits
+// sampling.ArgMax (reference model/sampling/argmax.go:4-18): first index of the strict maximum; a
+// NaN never wins and a NaN in position 0 keeps index 0. One CTA: 128256 logits are 0.5 MB, a few
+// microseconds from L2 right after the LM-head GEMV wrote them, and nothing is read back but the index.
+__global__ void __launch_bounds__(1024, 1) argmax_kernel(const float* __restrict__ v, int n, int* __restrict__ out) {
+  __shared__ float s_val[32];
+  __shared__ int s_idx[32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (n <= 0) { if (tid == 0) *out = 0; return; }
+  const float first = v[0];
+  if (first != first) { if (tid == 0) *out = 0; return; }   // NaN in position 0: nothing compares greater
+  float best = first;
+  int bi = 0;
+  for (int i = tid; i < n; i += 1024) {
+    const float x = v[i];
+    if (x > best) { best = x; bi = i; }   // indices rise within a thread: ties keep the earliest
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+  }
+  if (lane == 0) { s_val[warp] = best; s_idx[warp] = bi; }
+  __syncthreads();
+  if (warp == 0) {
+    best = s_val[lane]; bi = s_idx[lane];
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if (lane == 0) *out = bi;
+  }
+}
+int wv_launch_argmax(const float* d_logits, int n, int* d_out, cudaStream_t st) {
+  argmax_kernel<<<1, 1024, 0, st>>>(d_logits, n, d_out);
+  return cudaGetLastError() == cudaSuccess ? WV_OK : WV_ECUDA;
+}
+
 thread_local const WvPeers* wv_cur_peers = nullptr;
 
 // Copies n floats of this GPU's slice to the same position of every other rank's vector (the
