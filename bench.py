@@ -145,6 +145,84 @@ def run_reference(args, rank, world):
 
 
 # ------------------------------------------------------------------------------ product arm
+def decode_projections(torch, L, _lib, stream):
+    """Time of the projection GEMVs of one decoded token for Llama-8B shapes in Q4_K, chained as in the
+    model: 32 x [Q|K|V group, O, gate|up group, down] and the LM head followed by the greedy pick, all
+    in one CUDA graph. Norms, RoPE and attention are not part of this library yet and are left out,
+    so this is the GEMV share of a token, not a tokens/s claim for the whole model."""
+    import ctypes as C
+    fmt, hid, ffn, kv, vocab, layers = 8, 4096, 14336, 1024, 128256, 32   # Q4_K
+    shapes = {"q": (hid, hid), "k": (kv, hid), "v": (kv, hid), "o": (hid, hid), "gate": (ffn, hid), "up": (ffn, hid), "down": (hid, ffn)}
+    key = 0x40000
+    blocks, nbytes = [], 0
+    for _ in range(2):          # two distinct blocks alternate: 286 MB of weights, more than twice L2
+        blk = {}
+        for name, (r, c) in shapes.items():
+            w = torch.randn(r * c, device="cuda") * 0.02
+            key += 1
+            _lib.check(L.wv_pack_upload_dev(key, fmt, 1, 0, w.data_ptr(), r, c, None))
+            wb = C.c_uint64()
+            _lib.check(L.wv_blob_info(key, None, None, C.byref(wb), None, None))
+            blk[name] = key
+            nbytes += int(wb.value)
+            del w
+        blocks.append(blk)
+    w = torch.randn(vocab * hid, device="cuda") * 0.02
+    key += 1
+    _lib.check(L.wv_pack_upload_dev(key, fmt, 1, 0, w.data_ptr(), vocab, hid, None))
+    del w
+    head = key
+    wb = C.c_uint64()
+    _lib.check(L.wv_blob_info(head, None, None, C.byref(wb), None, None))
+    token_bytes = nbytes // 2 * layers + int(wb.value)
+    x = torch.randn(hid, device="cuda")
+    bufs = {n: torch.zeros(shapes[n][0], device="cuda") for n in shapes}
+    logits = torch.zeros(vocab, device="cuda")
+    pick = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def multi(keys, src, dsts, outs, st):
+        n = len(keys)
+        _lib.check(L.wv_matvec_dev_multi((C.c_uint64 * n)(*keys), n, src.data_ptr(), (C.c_void_p * n)(*[d.data_ptr() for d in dsts]),
+                                         1, hid, (C.c_int * n)(*outs), st))
+
+    def token(st):
+        cur = x
+        for layer in range(layers):
+            b = blocks[layer & 1]
+            multi([b["q"], b["k"], b["v"]], cur, [bufs["q"], bufs["k"], bufs["v"]], [hid, kv, kv], st)
+            _lib.check(L.wv_matvec_dev(b["o"], bufs["q"].data_ptr(), bufs["o"].data_ptr(), 1, hid, hid, st))
+            multi([b["gate"], b["up"]], bufs["o"], [bufs["gate"], bufs["up"]], [ffn, ffn], st)
+            _lib.check(L.wv_matvec_dev(b["down"], bufs["gate"].data_ptr(), bufs["down"].data_ptr(), 1, ffn, hid, st))
+            cur = bufs["down"]
+        _lib.check(L.wv_matvec_dev(head, cur.data_ptr(), logits.data_ptr(), 1, hid, vocab, st))
+        _lib.check(L.wv_argmax_dev(logits.data_ptr(), vocab, pick.data_ptr(), st))
+
+    with torch.cuda.stream(stream):
+        token(stream.cuda_stream)
+    stream.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream):
+        token(torch.cuda.current_stream().cuda_stream)
+    best = 1e30
+    with torch.cuda.stream(stream):
+        g.replay()
+        stream.synchronize()
+        for _ in range(5):
+            a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream); g.replay(); b_.record(stream)
+            stream.synchronize()
+            best = min(best, a.elapsed_time(b_))
+    del g
+    for blk in blocks:
+        for k in blk.values():
+            L.wv_blob_evict(k)
+    L.wv_blob_evict(head)
+    return {"model": "Llama-8B shapes (32 blocks: Q|K|V, O, gate|up, down; LM head 128256x4096; greedy pick)", "format": "Q4_K",
+            "launches_per_token": layers * 4 + 2, "packed_bytes_per_token": token_bytes, "ms_per_token": round(best, 4),
+            "gbs": round(token_bytes / best / 1e6, 1), "tokens_per_s_gemv_only": round(1e3 / best, 1),
+            "note": "projection GEMVs and the pick only; norms, RoPE and attention are outside this library and not timed"}
+
+
 def main():
     # NCCL prints its version line to stdout when NCCL_DEBUG asks for it; stdout carries the one JSON line
     os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
@@ -420,6 +498,8 @@ def main():
         gbs, cores, sec, total = cpu_leg(3, 1, sample, SHAPES[0])
         out["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
                                "sample": f"{len(sample)} formats ({','.join(f[0] for f in sample)}) at 4096x14336, 3 timed passes, SIMD-path caches prebuilt"}
+    if world == 1 and not args.quick and not args.formats:
+        out["decode_projections"] = decode_projections(torch, L, _lib, stream)
     print(json.dumps(out))
 
 

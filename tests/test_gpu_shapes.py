@@ -144,3 +144,38 @@ def test_lm_head_slice_row_shard(wv):
         y = np.zeros(n, np.float32)
         wv.quant.MatVec(blob, x, y)
         check(y, ob, x, refs=("simd",))
+
+
+def test_concurrent_host_callers(wv):
+    """Callers may be concurrent threads (the reference's goroutines): the synchronous entry serialises
+    on its staging buffers and every caller gets its own result."""
+    import threading
+    rows, cols = 512, 2048
+    q = wv.quant
+    jobs = []
+    for i, f in enumerate(["Q4_K", "Q8_0", "Q4_0", "IQ2_XS"]):
+        w, x = make_w(70 + i, rows, cols)
+        ob = O.pack(f, w, rows, cols)
+        jobs.append((to_product_blob(wv, ob), ob, x))
+    for b, _, x in jobs:                       # warm: uploads happen once
+        q.MatVec(b, x, np.zeros(rows, np.float32))
+    want = [(lambda y: (q.MatVec(b, x, y), y)[1])(np.zeros(rows, np.float32)) for b, _, x in jobs]
+    out = [[None] * 20 for _ in jobs]
+    errs = []
+
+    def worker(j):
+        try:
+            b, _, x = jobs[j]
+            for k in range(20):
+                y = np.zeros(rows, np.float32)
+                q.MatVec(b, x, y)
+                out[j][k] = y
+        except Exception as e:  # noqa: BLE001
+            errs.append(e)
+    ts = [threading.Thread(target=worker, args=(j,)) for j in range(len(jobs))]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    assert not errs, errs
+    for j in range(len(jobs)):
+        for k in range(20):
+            assert np.array_equal(out[j][k].view(np.uint32), want[j].view(np.uint32))

@@ -19,6 +19,8 @@
 //   weights.Store, New, FromBlob, packed wire         weights/store.go:14-66, from_blob.go:11-32, packed_wire.go:30-110
 //   dense.Layer, NewConfigured, Forward, MatVec*      layers/dense/dense.go:12-167, simd.go:571-614, webgpu.go:17-48
 //   resident-weight cache (Warm / Has / Clear / Bytes) webgpu/affine_cache.go:29-203
+//   sampling.ArgMax                                    model/sampling/argmax.go:4-18
+//   fused projection groups (Q|K|V, gate|up)           fusedgpu/shaders.go:59-222, mha/cpu.go:48-96, swiglu/cpu.go:29-52
 #pragma once
 #include <cmath>
 #include <cstdint>
@@ -302,6 +304,21 @@ inline Error MatVecCUDA(const weights::Store* s, const std::vector<float>& x, st
   return fromStatus("matvec", wv_matvec(s->Packed->Key(), x.data(), y.data(), batch, in, out));
 }
 
+// Projection group on one shared x (Q|K|V of mha, gate|up of swiglu): device pointers, asynchronous on `stream`;
+// stores of one format and column count run as one launch, any other mix as separate launches.
+inline Error MatVecGroupCUDA(const std::vector<const weights::Store*>& stores, const float* dx, const std::vector<float*>& dy,
+                             int batch, int in, void* stream = nullptr) {
+  const int n = (int)stores.size();
+  if (n < 1 || n > 4 || dy.size() != stores.size()) return errorf(WV_EARG, "dense: group of 1..4 stores with one output each");
+  uint64_t keys[4]; int outs[4]; float* ys[4];
+  for (int i = 0; i < n; i++) {
+    if (!stores[i] || !stores[i]->Packed) return errorf(WV_EARG, "dense: nil weights");
+    if (Error e = quant::EnsureResident(stores[i]->Packed.get())) return e;
+    keys[i] = stores[i]->Packed->Key(); outs[i] = stores[i]->Rows; ys[i] = dy[i];
+  }
+  return fromStatus("matvec_multi", wv_matvec_dev_multi(keys, n, dx, ys, batch, in, outs, stream));
+}
+
 // dense.MatVecPackedBlob (layers/dense/simd.go:571-614)
 inline Error MatVecPackedBlob(const quant::Blob* b, const std::vector<float>& x, std::vector<float>& y) {
   if (!b) return errorf(WV_EARG, "dense: nil packed blob");
@@ -352,4 +369,13 @@ std::tuple<TensorPtr<T>, TensorPtr<T>, Error> Forward(const Layer* l, const core
   return {nullptr, nullptr, errorf(WV_EFORMAT, std::string("dense: backend ") + core::BackendString(l->Exec.Backend_) + " is not provided by this library (cuda only)")};
 }
 }  // namespace dense
+
+namespace sampling {
+// sampling.ArgMax (model/sampling/argmax.go:4-18) over n device floats: first strict maximum, NaN never wins.
+inline std::pair<int, Error> ArgMax(const float* d_logits, int n, void* stream = nullptr) {
+  int idx = 0;
+  if (int rc = wv_argmax(d_logits, n, &idx, stream)) return {0, fromStatus("argmax", rc)};
+  return {idx, Error{}};
+}
+}  // namespace sampling
 }  // namespace welvet
