@@ -40,6 +40,17 @@ def test_status_codes_without_a_device():
     x = np.zeros(8, np.float32)
     assert L.wv_matvec(1, x.ctypes.data, x.ctypes.data, 1, 8, 8) == m.WV_EINIT  # no CPU fallback
     assert L.wv_blob_has(1) == 0 and L.wv_cache_bytes() == 0
+    # every compute entry fails the same way: nothing runs on the host
+    keys, outs, ptrs = (C.c_uint64 * 1)(1), (C.c_int * 1)(8), (C.c_void_p * 1)(x.ctypes.data)
+    idx, p, h = C.c_int(), C.c_void_p(), C.create_string_buffer(64)
+    assert L.wv_matvec_dev(1, x.ctypes.data, x.ctypes.data, 1, 8, 8, None) == m.WV_EINIT
+    assert L.wv_matvec_dev_static(1, x.ctypes.data, x.ctypes.data, 8, 8, None) == m.WV_EINIT
+    assert L.wv_matvec_dev_multi(keys, 1, x.ctypes.data, ptrs, 1, 8, outs, None) == m.WV_EINIT
+    assert L.wv_matvec_dev_gather(1, x.ctypes.data, ptrs, 1, 0, 0, 8, 8, None) == m.WV_EINIT
+    assert L.wv_argmax(x.ctypes.data, 8, C.byref(idx), None) == m.WV_EINIT
+    assert L.wv_gather_alloc(64, C.byref(p), h) == m.WV_EINIT
+    assert L.wv_unpack(1, x.ctypes.data) == m.WV_EINIT
+    assert L.wv_pack(2, 1, 0, x.ctypes.data, 1, 8, x.ctypes.data, None, None) == m.WV_EINIT
 
 
 @pytest.mark.parametrize("case", CASES, ids=case_id)
