@@ -290,7 +290,6 @@ __device__ __forceinline__ float idot_chunk(const FragT<F>& f, const XQRegs& x) 
   if constexpr (fi.kind == WK_KQUANT) {
     // scale bytes were remapped 0 -> 1 at upload (kquant.go:180-182: a zero group scale
     // decodes as d/255), so no test is needed here
-#ifdef WV_KQ_I2F
     // byte -> float through the conversion unit (one instruction with a byte selector) instead of
     // a byte permute on the integer pipe plus a subtract
     const float t = (float)(unsigned char)(f.pr[2]) * val[0] + (float)(unsigned char)(f.pr[2] >> 8) * val[1];
@@ -299,16 +298,6 @@ __device__ __forceinline__ float idot_chunk(const FragT<F>& f, const XQRegs& x) 
       const float mm = (float)(signed char)(f.pr[2] >> 16) * mt.z + (float)(signed char)(f.pr[2] >> 24) * mt.w;
       extra = (__uint_as_float(f.pr[1]) * (1.0f / 127.0f)) * mm;
     }
-#else
-    const float t = u8f(f.pr[2], 0) * val[0] + u8f(f.pr[2], 1) * val[1];
-    v = (__uint_as_float(f.pr[0]) * (1.0f / 255.0f)) * t;
-    if constexpr (fi.has_min) {
-      const unsigned mb = f.pr[2] ^ 0x80800000u;  // int8 -> biased uint8
-      const float mm = (__uint_as_float(__byte_perm(mb, 0x4B000000u, 0x7652)) - 8388736.0f) * mt.z +
-                       (__uint_as_float(__byte_perm(mb, 0x4B000000u, 0x7653)) - 8388736.0f) * mt.w;
-      extra = (__uint_as_float(f.pr[1]) * (1.0f / 127.0f)) * mm;
-    }
-#endif
   } else if constexpr (fi.kind == WK_CLASSIC || fi.kind == WK_AFFINE) {
     v = __uint_as_float(f.pr[0]) * val[0];
     if constexpr (fi.has_min) extra = __uint_as_float(f.pr[1]) * mt.y;
