@@ -294,6 +294,8 @@ def main():
             j["off"] = off
             off += j["rows"]
         gbufs = GatherBuffers(4 * off, rank, world, exchange)
+        gflags = GatherBuffers(4 * (world + 2), rank, world, exchange)
+        f_all = (C.c_void_p * world)(*gflags.ptrs)
         for j in jobs:
             j["y_all"] = gbufs.pointers(j["off"])
 
@@ -303,9 +305,16 @@ def main():
         else:
             _lib.check(L.wv_matvec_dev(j["key"], xs[j["cols"]].data_ptr(), j["y"].data_ptr(), 1, j["cols"], j["rows"], st))
 
+    def step_end(st):
+        # a step is complete on a rank when every rank's rows have arrived: arrival flags, on the device
+        if world > 1:
+            _lib.check(L.wv_gather_signal(f_all, world, rank, st))
+            _lib.check(L.wv_gather_wait(gflags.own, world, st))
+
     def step_plain():
         for j in jobs:
             launch(j, stream.cuda_stream)
+        step_end(stream.cuda_stream)
 
     with torch.cuda.stream(stream):
         step_plain()                      # first call per kernel sets its attributes (not capturable)
@@ -316,6 +325,7 @@ def main():
         cur = torch.cuda.current_stream().cuda_stream
         for j in jobs:
             launch(j, cur)
+        step_end(cur)
     launch_mode = "cuda graph"
 
     def run_step():
@@ -354,7 +364,7 @@ def main():
         dist.all_reduce(t)
         full_bytes = float(t.item())
     value = full_bytes / (ms_step * 1e-3) / 1e9
-    launches_per_step = len(jobs)   # 4096 / 14336 columns take the TMA-fed kernel: one launch per GEMV
+    launches_per_step = len(jobs) + (2 if world > 1 else 0)   # one launch per GEMV (+ the two flag kernels of a sharded step)
 
     gather_ok = None
     if world > 1:
@@ -378,10 +388,14 @@ def main():
         gather_ok = bool(t.item() == 1.0)
         # unmap the peers' buffers everywhere before any rank frees its own, then leave together
         graph = None
+        if L.wv_device_status() != 0:
+            gather_ok = False
         gbufs.close_peers()
+        gflags.close_peers()
         torch.cuda.synchronize()
         dist.barrier()
         gbufs.free_own()
+        gflags.free_own()
         dist.destroy_process_group()
     if rank != 0:
         return
@@ -471,7 +485,7 @@ def main():
                    "weights": "N(0,0.02^2) seed 2", "activations": "N(0,1) seed 1",
                    "l2": "inputs larger than L2: one step streams %.0f MB of distinct packed weights" % (full_bytes / 1e6),
                    "sharding": ("rows split evenly across ranks; each rank's GEMV kernels store their rows into every rank's y "
-                                "(peer mappings, no collective call); ranks synchronise around the timed region; gathered y verified: %s" % gather_ok)
+                                "(peer mappings, no collective call); every step ends with on-device arrival flags; gathered y verified: %s" % gather_ok)
                    if world > 1 else "single GPU",
                    "launch": launch_mode,
                    "pct_of_8TBs": round(100 * value / NOMINAL_HBM_GBS, 1)},

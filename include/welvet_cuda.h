@@ -141,6 +141,17 @@ int wv_gather_alloc(size_t bytes, void** dptr, unsigned char handle[64]);
 int wv_gather_open(const unsigned char handle[64], void** dptr);
 int wv_gather_close(void* dptr);
 int wv_gather_free(void* dptr);
+/* Arrival flags for chained steps, so that a step's consumers need no host barrier: each rank owns a flag buffer of
+ * world + 2 unsigned words (wv_gather_alloc, zero-filled; mapped by the peers like the output vectors).
+ * wv_gather_signal, enqueued after this rank's gather GEMVs of a step, bumps this rank's step counter and stores it
+ * into word `rank` of every rank's flags (after a system-scope fence: the rows written before it are visible first).
+ * wv_gather_wait, enqueued before the kernels that read y, bumps the local wait counter and holds the stream until all
+ * `world` words have reached it. The wait is bounded (a fraction of a second): when it runs out the kernel records a code,
+ * returns, and wv_device_status() reports WV_ETIMEOUT; the context stays usable. Both are plain kernels and keep their
+ * counters on the device, so a captured graph can be replayed. A rank that has passed the wait of step k may already
+ * store rows of step k + 1 while a slower rank still reads step k: alternate two sets of output vectors between steps. */
+int wv_gather_signal(unsigned* const* flags_all, int world, int rank, void* stream);
+int wv_gather_wait(unsigned* flags_own, int world, void* stream);
 /* Copy `bytes` from a gather buffer (own or mapped) to host memory after synchronising `stream`. */
 int wv_gather_read(const void* dptr, size_t offset_bytes, void* host, size_t bytes, void* stream);
 

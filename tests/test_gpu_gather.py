@@ -58,6 +58,38 @@ def test_gather_epilogue_two_emulated_ranks(wv, case):
             b.close()
 
 
+def test_arrival_flags_in_stream_order_and_timeout(wv):
+    """Two emulated ranks on one stream: both signal, then both waits pass at once (nothing on one GPU ever waits
+    for work queued behind it). A wait that nobody signals runs out, is reported through wv_device_status and
+    leaves the context usable."""
+    L = wv._lib.lib()
+    world = 2
+    flags = [wv.dense.GatherBuffers(4 * (world + 2), 0, 1) for _ in range(world)]
+    try:
+        f_all = (C.c_void_p * world)(*[f.own for f in flags])
+        for step in range(1, 4):
+            for r in range(world):
+                wv._lib.check(L.wv_gather_signal(f_all, world, r, None))
+            for r in range(world):
+                wv._lib.check(L.wv_gather_wait(flags[r].own, world, None))
+            torch.cuda.synchronize()
+            assert L.wv_device_status() == 0
+            for r in range(world):
+                words = flags[r].read(0, world + 2).view(np.uint32)
+                assert list(words) == [step, step, step, step]
+        # rank 0 waits for a step that rank 1 never signals
+        wv._lib.check(L.wv_gather_signal(f_all, world, 0, None))
+        wv._lib.check(L.wv_gather_wait(flags[0].own, world, None))
+        torch.cuda.synchronize()
+        assert L.wv_device_status() == wv._lib.WV_ETIMEOUT
+        assert L.wv_device_status() == 0                      # reported once
+        y = torch.arange(8, dtype=torch.float32, device="cuda")
+        assert wv.sampling.ArgMaxCUDA(y.data_ptr(), 8) == 7   # the context still works
+    finally:
+        for f in flags:
+            f.close()
+
+
 def test_gather_argument_errors(wv):
     L = wv._lib.lib()
     y_all = (C.c_void_p * 1)(0)
@@ -100,8 +132,29 @@ for slot, f in enumerate(["Q4_K", "Q4_0", "Q8_0"]):
     dist.barrier()                      # every rank's kernel has finished: all slices are in place
     got = bufs.read(slot * rows, rows)
     ok = ok and np.array_equal(got.view(np.uint32), ref.cpu().numpy().view(np.uint32))
+# chained steps ordered by arrival flags only: gather GEMV -> signal -> wait -> pick over the whole gathered vector
+flags = wv.dense.GatherBuffers(4 * (world + 2), rank, world, exchange)
+f_all = (C.c_void_p * world)(*flags.ptrs)
+picks = torch.zeros(6, dtype=torch.int32, device="cuda")
+refs = []
+for step in range(6):
+    slot = step % 3
+    x = np.random.default_rng(100 + step).normal(0, 1, cols).astype(np.float32)
+    dx = torch.from_numpy(x).cuda()
+    ref = torch.zeros(rows, device="cuda")
+    wv._lib.check(L.wv_matvec_dev(200 + slot, dx.data_ptr(), ref.data_ptr(), 1, cols, rows, None))
+    refs.append(int(torch.argmax(ref).item()))
+    L.wv_shard_range(rows, rank, world, C.byref(r0), C.byref(r1))
+    wv._lib.check(L.wv_matvec_dev_gather(100 + slot, dx.data_ptr(), bufs.pointers(slot * rows), world, rank, r0.value, cols, r1.value - r0.value, None))
+    wv._lib.check(L.wv_gather_signal(f_all, world, rank, None))
+    wv._lib.check(L.wv_gather_wait(flags.own, world, None))
+    wv._lib.check(L.wv_argmax_dev(bufs.own + 4 * slot * rows, rows, picks.data_ptr() + 4 * step, None))
+torch.cuda.synchronize()
+ok = ok and L.wv_device_status() == 0 and picks.cpu().tolist() == refs
 dist.barrier()
-bufs.close()
+flags.close_peers(); bufs.close_peers()
+dist.barrier()
+flags.free_own(); bufs.free_own()
 dist.destroy_process_group()
 print("RANK", rank, "OK" if ok else "MISMATCH")
 sys.exit(0 if ok else 1)

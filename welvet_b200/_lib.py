@@ -18,7 +18,7 @@ SYMBOLS = [
     "wv_blob_has", "wv_blob_evict", "wv_cache_clear", "wv_cache_bytes", "wv_cache_set_limit",
     "wv_blob_info", "wv_matvec", "wv_matvec_dev", "wv_unpack", "wv_unpack_dev",
     "wv_pack_sizes", "wv_pack", "wv_pack_upload_dev", "wv_set_tuning", "wv_set_tma_tuning", "wv_device_status", "wv_matvec_dev_static",
-    "wv_argmax_dev", "wv_argmax", "wv_matvec_dev_multi", "wv_matvec_dev_gather", "wv_gather_alloc", "wv_gather_open", "wv_gather_close", "wv_gather_free", "wv_gather_read",
+    "wv_argmax_dev", "wv_argmax", "wv_matvec_dev_multi", "wv_matvec_dev_gather", "wv_gather_alloc", "wv_gather_open", "wv_gather_close", "wv_gather_free", "wv_gather_read", "wv_gather_signal", "wv_gather_wait",
 ]
 
 WV_OK, WV_ESHAPE, WV_EFORMAT, WV_ENOMEM, WV_ECUDA, WV_ETIMEOUT, WV_ENOTFOUND, WV_EINIT, WV_EARG = (
@@ -75,6 +75,8 @@ def lib() -> C.CDLL:
         L.wv_gather_open.argtypes = [C.c_char_p, C.POINTER(vp)]
         L.wv_gather_close.argtypes = [vp]
         L.wv_gather_free.argtypes = [vp]
+        L.wv_gather_signal.argtypes = [C.POINTER(vp), i, i, vp]
+        L.wv_gather_wait.argtypes = [vp, i, vp]
         L.wv_gather_read.argtypes = [vp, sz, vp, sz, vp]
         L.wv_unpack.argtypes = [u64, vp]
         L.wv_unpack_dev.argtypes = [u64, vp, vp]

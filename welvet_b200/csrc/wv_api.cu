@@ -478,6 +478,23 @@ extern "C" int wv_matvec_dev_gather(uint64_t key, const float* dx, float* const*
   return rc;
 }
 
+int wv_launch_gather_signal(unsigned* const* flags_all, int world, int rank, cudaStream_t st);   // wv_gemv.cu
+int wv_launch_gather_wait(unsigned* flags_own, int world, cudaStream_t st);
+
+extern "C" int wv_gather_signal(unsigned* const* flags_all, int world, int rank, void* stream) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!flags_all || world < 1 || world > WV_MAX_PEERS || rank < 0 || rank >= world) { wv_set_error("wv_gather_signal: bad argument"); return WV_EARG; }
+  for (int q = 0; q < world; q++) if (!flags_all[q]) { wv_set_error("wv_gather_signal: flags_all[%d] is null", q); return WV_EARG; }
+  return wv_launch_gather_signal(flags_all, world, rank, static_cast<cudaStream_t>(stream));
+}
+extern "C" int wv_gather_wait(unsigned* flags_own, int world, void* stream) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!flags_own || world < 1 || world > WV_MAX_PEERS) { wv_set_error("wv_gather_wait: bad argument"); return WV_EARG; }
+  return wv_launch_gather_wait(flags_own, world, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int wv_gather_alloc(size_t bytes, void** dptr, unsigned char handle[64]) {
   int rc = ensure_init();
   if (rc) return rc;

@@ -568,6 +568,48 @@ __global__ void scatter_slice_kernel(const WvPeers peers, int n) {
   }
 }
 
+// ------------------------------------------------------------------ arrival flags of the gather
+struct WvFlagPeers { unsigned* f[WV_MAX_PEERS]; int n, self; };
+
+// One thread per rank: this rank's new step number goes to word `self` of every rank's flags.
+__global__ void gather_signal_kernel(const WvFlagPeers p) {
+  __shared__ unsigned s_epoch;
+  if (threadIdx.x == 0) s_epoch = ++p.f[p.self][p.n];          // word n: steps signalled by this rank
+  __syncthreads();
+  if ((int)threadIdx.x < p.n) {
+    __threadfence_system();                                     // the rows stored by the preceding kernels first
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.f[threadIdx.x] + p.self), "r"(s_epoch) : "memory");
+  }
+}
+// One thread per rank polls its word until it reaches this rank's new wait number; bounded.
+__global__ void gather_wait_kernel(unsigned* flags, int n, int* err) {
+  __shared__ unsigned s_epoch;
+  if (threadIdx.x == 0) s_epoch = ++flags[n + 1];               // word n + 1: steps waited for by this rank
+  __syncthreads();
+  if ((int)threadIdx.x < n) {
+    bool ok = false;
+    for (int i = 0; i < (1 << 17) && !ok; i++) {
+      unsigned v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + threadIdx.x) : "memory");
+      ok = (int)(v - s_epoch) >= 0;
+      if (!ok) __nanosleep(256);
+    }
+    if (!ok) atomicCAS_system(err, 0, 700 + (int)threadIdx.x);
+  }
+}
+int wv_launch_gather_signal(unsigned* const* flags_all, int world, int rank, cudaStream_t st) {
+  WvFlagPeers p{};
+  p.n = world; p.self = rank;
+  for (int q = 0; q < world; q++) p.f[q] = flags_all[q];
+  gather_signal_kernel<<<1, 32, 0, st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? WV_OK : WV_ECUDA;
+}
+int* wv_tma_err_ptr();
+int wv_launch_gather_wait(unsigned* flags_own, int world, cudaStream_t st) {
+  gather_wait_kernel<<<1, 32, 0, st>>>(flags_own, world, wv_tma_err_ptr());
+  return cudaGetLastError() == cudaSuccess ? WV_OK : WV_ECUDA;
+}
+
 // Kernels that load planes through registers (and the FormatNone streaming kernel).
 static int launch_gemv_regs(const WvDevBlob& b, const float* dx, float* dy, int batch, int row_begin, int row_end, cudaStream_t st) {
   switch (b.format) {
