@@ -141,10 +141,22 @@ def run_reference(args, rank, world):
            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": desc},
            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
            "gpu_launches": 0}
-    print(json.dumps(out))
+    emit(out)
 
 
 # ------------------------------------------------------------------------------ product arm
+_STDOUT_FD = None
+
+
+def emit(obj):
+    line = (json.dumps(obj) + "\n").encode()
+    if _STDOUT_FD is None:
+        sys.stdout.write(line.decode()); sys.stdout.flush()
+    else:
+        sys.stdout.flush()
+        os.write(_STDOUT_FD, line)
+
+
 def decode_projections(torch, L, _lib, stream):
     """Time of the projection GEMVs of one decoded token for Llama-8B shapes in Q4_K, chained as in the
     model: 32 x [Q|K|V group, O, gate|up group, down] and the LM head followed by the greedy pick, all
@@ -224,8 +236,12 @@ def decode_projections(torch, L, _lib, stream):
 
 
 def main():
-    # NCCL prints its version line to stdout when NCCL_DEBUG asks for it; stdout carries the one JSON line
-    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+    # stdout carries the one JSON line and nothing else: libraries that print there (NCCL's version
+    # banner, for one) are sent to stderr, the line itself goes to the saved descriptor
+    global _STDOUT_FD
+    sys.stdout.flush()
+    _STDOUT_FD = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -514,7 +530,7 @@ def main():
                                "sample": f"{len(sample)} formats ({','.join(f[0] for f in sample)}) at 4096x14336, 3 timed passes, SIMD-path caches prebuilt"}
     if world == 1 and not args.quick and not args.formats:
         out["decode_projections"] = decode_projections(torch, L, _lib, stream)
-    print(json.dumps(out))
+    emit(out)
 
 
 if __name__ == "__main__":
