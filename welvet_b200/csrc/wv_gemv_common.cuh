@@ -133,6 +133,28 @@ __device__ __forceinline__ float chunk_value(const FragT<F>& f, const float4 (&x
 }
 
 
+// IQ4_NL in the bulk-copy kernel. The grid sits in shared memory as [16 codes][64 floats] and lane l
+// uses float l of each row, so the byte offset of a code's entry is one byte permute (byte 1 = code,
+// byte 0 = 4 * lane) and lanes never collide on a bank.
+template <int F>
+__device__ __forceinline__ float chunk_value_tbl(const FragT<F>& f, const float4 (&xr)[8], const unsigned char* tbl, unsigned lane4) {
+  static_assert(wv_fmt_info(F).table && wv_fmt_info(F).bits_lo == 4, "4-bit table format");
+  float2 a0 = make_float2(0.f, 0.f), a1 = a0, b0 = a0, b1 = a0;
+#pragma unroll
+  for (int k = 0; k < 8; k++) {
+    const unsigned bytes = (f.lo[k >> 1] >> (4 * (k & 1))) & 0x0F0F0F0Fu;
+    float2 q01, q23;
+    q01.x = *reinterpret_cast<const float*>(tbl + __byte_perm(bytes, lane4, 0x5504));
+    q01.y = *reinterpret_cast<const float*>(tbl + __byte_perm(bytes, lane4, 0x5514));
+    q23.x = *reinterpret_cast<const float*>(tbl + __byte_perm(bytes, lane4, 0x5524));
+    q23.y = *reinterpret_cast<const float*>(tbl + __byte_perm(bytes, lane4, 0x5534));
+    const float2 x01 = make_float2(xr[k].x, xr[k].y), x23 = make_float2(xr[k].z, xr[k].w);
+    if (k & 1) { b0 = __ffma2_rn(q01, x01, b0); b1 = __ffma2_rn(q23, x23, b1); }
+    else { a0 = __ffma2_rn(q01, x01, a0); a1 = __ffma2_rn(q23, x23, a1); }
+  }
+  return __uint_as_float(f.pr[0]) * (((a0.x + a0.y) + (a1.x + a1.y)) + ((b0.x + b0.y) + (b1.x + b1.y)));
+}
+
 // ------------------------------------------------------------------ integer-dot chunk math
 // Activations arrive as block fixed point (see xquant_kernel): per 32 columns
 // X_j = rint(x_j * 2^(22-e)), 2^e > max|x| of the block, split into three byte limbs

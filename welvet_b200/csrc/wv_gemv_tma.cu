@@ -151,7 +151,7 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   }
   if constexpr (fi.table) {
     float* tbl = reinterpret_cast<float*>(smem + g.red_off) + 2 * g.nrg * g.nwc * 32;
-    for (int i = tid; i < 512; i += TMA_THREADS) tbl[i] = c_grid4nl[i >> 5];
+    for (int i = tid; i < 1024; i += TMA_THREADS) tbl[i] = c_grid4nl[i >> 6];   // [16 codes][64 floats]
   }
   __syncthreads();
 
@@ -255,11 +255,11 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   if (rg >= g.nrg) return;
   XQRegs xr;
   float4 xfr[8];
-  const float* tbl = nullptr;
+  const unsigned char* tbl = nullptr;
   {
     const float* xc = reinterpret_cast<const float*>(smem + g.x_off) + (size_t)c * 33;
     if constexpr (fi.table) {
-      tbl = reinterpret_cast<const float*>(smem + g.red_off) + 2 * g.nrg * g.nwc * 32 + lane;
+      tbl = smem + g.red_off + 2u * g.nrg * g.nwc * 32 * 4;
 #pragma unroll
       for (int k = 0; k < 8; k++) xfr[k] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (live) {
@@ -369,7 +369,7 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
       // No per-row branch: the RT chunk-rows form one block of independent dependency chains.
       // Lanes past the last chunk hold zeroed activations and contribute exactly 0.
       (void)lr;
-      if constexpr (fi.table) v[rr] = chunk_value<F>(fr[rr], xfr, make_float2(0.f, 0.f), tbl);
+      if constexpr (fi.table) v[rr] = chunk_value_tbl<F>(fr[rr], xfr, tbl, (unsigned)lane * 4u);
       else v[rr] = idot_chunk<F>(fr[rr], xr);
     }
     // Transposing reduction: RT row sums per lane -> every lane ends with the warp total of one
@@ -464,7 +464,7 @@ static int launch_tma(const WvDevBlob* bl, int nb, const float* dx, float* const
   for (int i = 0; i < 5; i++) { g.off[i] = off; off = align128(off + g.rb[i] * g.tr); }
   g.stage_bytes = off;
   const unsigned xbytes = align128((unsigned)g.cpr * 132u);
-  const unsigned fixed = xbytes + align128(2u * g.nrg * g.nwc * 32 * 4 + (fi.table ? 2048u : 0u)) + 2 * TMA_MAX_STAGES * 8 + 128;
+  const unsigned fixed = xbytes + align128(2u * g.nrg * g.nwc * 32 * 4 + (fi.table ? 4096u : 0u)) + 2 * TMA_MAX_STAGES * 8 + 128;
   const unsigned avail = 225u * 1024u;  // 227 KB per CTA minus static shared memory and slack
   if (g.stage_bytes * 2 + fixed > avail) return 1;
   int ns = (int)((avail - fixed) / g.stage_bytes);
@@ -474,7 +474,7 @@ static int launch_tma(const WvDevBlob* bl, int nb, const float* dx, float* const
   g.nstage = ns;
   g.x_off = g.stage_bytes * ns;
   g.red_off = g.x_off + xbytes;
-  g.bar_off = align128(g.red_off + 2u * g.nrg * g.nwc * 32 * 4 + (fi.table ? 2048u : 0u));
+  g.bar_off = align128(g.red_off + 2u * g.nrg * g.nwc * 32 * 4 + (fi.table ? 4096u : 0u));
   const size_t smem = g.bar_off + 2 * TMA_MAX_STAGES * 8;
 
   auto kern = gemv_tma_kernel<F, RT, PF>;
