@@ -165,11 +165,17 @@ __device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap* tm,
                ::"r"(dst), "l"(reinterpret_cast<unsigned long long>(tm)), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
 }
 
-template <int F, int PW, int NSEG>
+// Peer vectors only in the instantiation that stores to them: the plain GEMV keeps a short parameter list.
+struct MmaNoPeers {};
+template <bool P> struct MmaPeerArgs { using type = MmaNoPeers; };
+template <> struct MmaPeerArgs<true> { using type = WvPeers; };
+
+template <int F, int PW, int NSEG, bool PEERS>
 __global__ void __launch_bounds__(MMA_THREADS, 1)
 gemv_mma_kernel(const WvDevBlob b, const float* __restrict__ xf, float* __restrict__ y, int row_begin, const MmaGeom g,
                 int* __restrict__ err, const __grid_constant__ CUtensorMap tm_lo, const __grid_constant__ CUtensorMap tm_hi,
-                const __grid_constant__ CUtensorMap tm_p0, const __grid_constant__ CUtensorMap tm_p1, const WvPeers peers) {
+                const __grid_constant__ CUtensorMap tm_p0, const __grid_constant__ CUtensorMap tm_p1,
+                const typename MmaPeerArgs<PEERS>::type peers) {
   constexpr WvFmtInfo fi = wv_fmt_info(F);
   constexpr int BL = fi.bits_lo, BH = fi.bits_hi;
   constexpr bool INT_MID = MmaCfg<F>::INT_MID, SIGNED_A = MmaCfg<F>::SIGNED_A;
@@ -430,8 +436,11 @@ gemv_mma_kernel(const WvDevBlob b, const float* __restrict__ xf, float* __restri
       for (int q = 0; q < MMA_WARPS; q++) sum += base[q * 16];
       const int row = mt * 16 + lane;
       if (row < band) {
-        if (peers.n == 0) yb[row] = sum;
-        else for (int q = 0; q < peers.n; q++) peers.y[q][row_begin + c_lo + row] = sum;   // own and peers' copies of y
+        if constexpr (PEERS) {
+          for (int q = 0; q < peers.n; q++) peers.y[q][row_begin + c_lo + row] = sum;   // own and peers' copies of y
+        } else {
+          yb[row] = sum;
+        }
       }
     }
     par ^= 1;
@@ -548,23 +557,36 @@ static int launch_mma(const WvDevBlob& b, const float* dx, float* dy, int batch,
     maps = it->second;
   }
 
-  auto kern = gemv_mma_kernel<F, PW, NSEG>;
-  static unsigned attr_mask = 0;
-  int dev = 0; cudaGetDevice(&dev);
-  if (!(attr_mask & (1u << dev))) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) != cudaSuccess) { wv_set_error("gemv (mma): cannot raise the shared-memory limit"); return WV_ECUDA; }
-    attr_mask |= 1u << dev;
-  }
   g.nrows = re - rb_;
   const int total_mt = (g.nrows + 15) / 16;
   int grid = wv_sm_count();
   if (grid > total_mt) grid = total_mt;
   g.mt_base = total_mt / grid;
   g.mt_rem = total_mt % grid;
-  WvPeers peers{};
-  if (wv_cur_peers) { if (batch != 1) return WV_ESHAPE; peers = *wv_cur_peers; }
-  cudaError_t e = launch_pdl(kern, dim3(grid, batch), dim3(MMA_THREADS), smem, st, b, dx, dy, rb_, g, wv_tma_err_ptr(),
-                             maps.m[0], maps.m[1], maps.m[2], maps.m[3], peers);
+  int dev = 0; cudaGetDevice(&dev);
+  cudaError_t e;
+  if (!wv_cur_peers) {
+    auto kern = gemv_mma_kernel<F, PW, NSEG, false>;
+    static unsigned attr_mask = 0;
+    if (!(attr_mask & (1u << dev))) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) != cudaSuccess) { wv_set_error("gemv (mma): cannot raise the shared-memory limit"); return WV_ECUDA; }
+      attr_mask |= 1u << dev;
+    }
+    e = launch_pdl(kern, dim3(grid, batch), dim3(MMA_THREADS), smem, st, b, dx, dy, rb_, g, wv_tma_err_ptr(),
+                   maps.m[0], maps.m[1], maps.m[2], maps.m[3], MmaNoPeers{});
+  } else if constexpr (PW != 4) {
+    return 1;   // the peer-storing variant exists for the default pairs-per-warp only
+  } else {
+    if (batch != 1) return WV_ESHAPE;
+    auto kern = gemv_mma_kernel<F, PW, NSEG, true>;
+    static unsigned attr_mask = 0;
+    if (!(attr_mask & (1u << dev))) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) != cudaSuccess) { wv_set_error("gemv (mma): cannot raise the shared-memory limit"); return WV_ECUDA; }
+      attr_mask |= 1u << dev;
+    }
+    e = launch_pdl(kern, dim3(grid, batch), dim3(MMA_THREADS), smem, st, b, dx, dy, rb_, g, wv_tma_err_ptr(),
+                   maps.m[0], maps.m[1], maps.m[2], maps.m[3], *wv_cur_peers);
+  }
   if (e != cudaSuccess) { wv_set_error("gemv (mma) launch: %s", cudaGetErrorString(e)); return WV_ECUDA; }
   return WV_OK;
 }

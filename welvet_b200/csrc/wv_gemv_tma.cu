@@ -35,6 +35,7 @@ struct TmaGeom {
   unsigned stage_bytes;
   unsigned off[5];   // lo, hi, p0, p1, km section offsets inside a stage
   unsigned rb[5];    // bytes per row of each plane (0 = plane absent)
+  int rows_base, rows_rem;  // single matrix: CTA b owns rows_base (+1 if b < rows_rem) consecutive rows
   int lead;          // tiles issued before the producer waits for the activation loads to be on their way
   unsigned x_off;    // staged activations: 33 floats per chunk (32 + one of padding)
   unsigned red_off;  // float red[2][nrg][nwc][32]
@@ -51,6 +52,16 @@ struct TmaGroup {
   const void* plane[TMA_MAX_GROUP][5];                      // lo, hi, p0, p1, km
   float* y[TMA_MAX_GROUP];
 };
+
+// What only the grouped launch and the peer-storing epilogue need. The plain GEMV is instantiated
+// without it: the extra parameters and loop nest cost 0.3-0.6 us per launch when they were always there.
+struct TmaExt {
+  TmaGroup grp;
+  WvPeers peers;
+};
+struct TmaNoExt {};
+template <bool EXT> struct TmaExtArgs { using type = TmaNoExt; };
+template <> struct TmaExtArgs<true> { using type = TmaExt; };
 
 // Sticky code of the first bounded wait that ran out, in mapped pinned host memory so that the
 // host can poll it without a CUDA call.
@@ -118,10 +129,10 @@ __device__ __forceinline__ void load_frag_smem(FragT<F>& f, const LaneOff& a) {
   }
 }
 
-template <int F, int RT, bool PREFETCH>
+template <int F, int RT, bool PREFETCH, bool EXT>
 __global__ void __launch_bounds__(TMA_THREADS, 1)
-gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* __restrict__ xf, const TmaGroup grp,
-                int row_begin, int row_end, const TmaGeom g, int* __restrict__ err, const WvPeers peers) {
+gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* __restrict__ xf, float* __restrict__ y,
+                int row_begin, int row_end, const TmaGeom g, int* __restrict__ err, const typename TmaExtArgs<EXT>::type ext) {
   constexpr WvFmtInfo fi = wv_fmt_info(F);
   constexpr int BL = fi.bits_lo;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -132,11 +143,16 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   const int bid = blockIdx.x;
   int band, c_lo, c_hi, ntiles;
   auto set_band = [&](int i) {
-    band = grp.rows_base[i] + (bid < grp.rows_rem[i] ? 1 : 0);
-    c_lo = bid * grp.rows_base[i] + min(bid, grp.rows_rem[i]);
+    int rbase = g.rows_base, rrem = g.rows_rem;
+    if constexpr (EXT) { rbase = ext.grp.rows_base[i]; rrem = ext.grp.rows_rem[i]; }
+    band = rbase + (bid < rrem ? 1 : 0);
+    c_lo = bid * rbase + min(bid, rrem);
     c_hi = c_lo + band;
     ntiles = (band + g.tr - 1) / g.tr;
   };
+  int nmat = 1;
+  if constexpr (EXT) nmat = ext.grp.n;
+  (void)y;
   (void)row_end; (void)xqg;
   const unsigned bar0 = smem_u32(smem + g.bar_off);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
@@ -158,6 +174,7 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   if (warp == TMA_CONSUMER_WARPS) {
     // ------------------------------------------------------------ producer
     // One thread issues the copies; the other lanes of the warp have nothing to do.
+    const void* src[5] = {b.lo, b.hi, b.p0, b.p1, b.km};
     bool dead = false;
     int issued = 0;        // tiles issued so far, over all matrices
     int ps = 0;            // stage of the tile being issued
@@ -182,7 +199,9 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
       const unsigned dst = smem_u32(smem) + (unsigned)s * g.stage_bytes;
 #pragma unroll
       for (int i = 0; i < 5; i++) {
-        if (g.rb[i]) bulk_g2s(dst + g.off[i], (const unsigned char*)grp.plane[bi][i] + (size_t)(row_begin + r0) * g.rb[i], g.rb[i] * nr, full_bar(s));
+        const void* pl = src[i];
+        if constexpr (EXT) pl = ext.grp.plane[bi][i];
+        if (g.rb[i]) bulk_g2s(dst + g.off[i], (const unsigned char*)pl + (size_t)(row_begin + r0) * g.rb[i], g.rb[i] * nr, full_bar(s));
       }
       WV_STAMP_ANY(40 + issued);
       issued++;
@@ -190,7 +209,7 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
     };
     if (lane == 0) {
       bool held = false;
-      for (bi = 0; bi < grp.n && !dead; bi++) {
+      for (bi = 0; bi < nmat && !dead; bi++) {
         set_band(bi);
         for (int t = 0; t < ntiles && !dead; t++) {
           if (!held && issued >= g.lead) {
@@ -297,8 +316,14 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
       const int n = batch_base + lane;
       const int row = c_lo + (n / RT) * g.tr + rg * RT + (n % RT);
       if (n < nslots && (n / RT) * g.tr + rg * RT + (n % RT) < band && rg * RT + (n % RT) < g.tr) {
-        if (peers.n == 0) yb[row] = sum;
-        else for (int q = 0; q < peers.n; q++) peers.y[q][row_begin + row] = sum;   // own and peers' copies of y
+        bool stored = false;
+        if constexpr (EXT) {
+          if (ext.peers.n) {
+            for (int q = 0; q < ext.peers.n; q++) ext.peers.y[q][row_begin + row] = sum;   // own and peers' copies of y
+            stored = true;
+          }
+        }
+        if (!stored) yb[row] = sum;
       }
     }
     par ^= 1;
@@ -339,10 +364,11 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
     if (++fs == g.nstage) { fs = 0; fpar ^= 1u; }
   };
 
-  for (int bi = 0; bi < grp.n; bi++) {   // one matrix after the other; ring position and x registers carry over
+  for (int bi = 0; bi < nmat; bi++) {   // one matrix after the other; ring position and x registers carry over
   set_band(bi);
   nslots = ntiles * RT;
-  yb = grp.y[bi] + (size_t)blockIdx.y * grp.rows[bi] + row_begin;
+  if constexpr (EXT) yb = ext.grp.y[bi] + (size_t)blockIdx.y * ext.grp.rows[bi] + row_begin;
+  else yb = y + (size_t)blockIdx.y * b.rows + row_begin;
   FragT<F> nxt[PREFETCH ? RT : 1];
   if constexpr (PREFETCH) { if (ntiles > 0) { wait_tile(true); fetch_tile(nxt); } }
   WV_STAMP(3);
@@ -477,29 +503,45 @@ static int launch_tma(const WvDevBlob* bl, int nb, const float* dx, float* const
   g.bar_off = align128(g.red_off + 2u * g.nrg * g.nwc * 32 * 4 + (fi.table ? 4096u : 0u));
   const size_t smem = g.bar_off + 2 * TMA_MAX_STAGES * 8;
 
-  auto kern = gemv_tma_kernel<F, RT, PF>;
-  static unsigned attr_mask = 0;
-  int dev = 0; cudaGetDevice(&dev);
-  if (!(attr_mask & (1u << dev))) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) != cudaSuccess) { wv_set_error("gemv (tma): cannot raise the shared-memory limit"); return WV_ECUDA; }
-    attr_mask |= 1u << dev;
-  }
   int grid = wv_sm_count();
-  TmaGroup grp{};
-  grp.n = nb;
   if (nb == 1 && grid > re - rb_) grid = re - rb_;
-  for (int i = 0; i < nb; i++) {
-    const int nrows = nb == 1 ? re - rb_ : bl[i].rows;
-    grp.rows[i] = bl[i].rows;
-    grp.rows_base[i] = nrows / grid;
-    grp.rows_rem[i] = nrows % grid;
-    grp.plane[i][0] = bl[i].lo; grp.plane[i][1] = bl[i].hi; grp.plane[i][2] = bl[i].p0; grp.plane[i][3] = bl[i].p1; grp.plane[i][4] = bl[i].km;
-    grp.y[i] = dys[i];
-  }
+  g.rows_base = (re - rb_) / grid;
+  g.rows_rem = (re - rb_) % grid;
   const uint4* xq = nullptr;  // activations are quantised inside the kernel
-  WvPeers peers{};
-  if (wv_cur_peers) { if (batch != 1 || nb != 1) return WV_ESHAPE; peers = *wv_cur_peers; }
-  cudaError_t e = launch_pdl(kern, dim3(grid, batch), dim3(TMA_THREADS), smem, st, b, xq, dx, grp, rb_, re, g, g_err_dev, peers);
+  int dev = 0; cudaGetDevice(&dev);
+  cudaError_t e;
+  if (nb == 1 && !wv_cur_peers) {
+    auto kern = gemv_tma_kernel<F, RT, PF, false>;
+    static unsigned attr_mask = 0;
+    if (!(attr_mask & (1u << dev))) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) != cudaSuccess) { wv_set_error("gemv (tma): cannot raise the shared-memory limit"); return WV_ECUDA; }
+      attr_mask |= 1u << dev;
+    }
+    e = launch_pdl(kern, dim3(grid, batch), dim3(TMA_THREADS), smem, st, b, xq, dx, dys[0], rb_, re, g, g_err_dev, TmaNoExt{});
+  } else {
+    if constexpr (RT == 4 && !PF) {   // the grouped / peer-storing variant exists for the default configuration only
+      auto kern = gemv_tma_kernel<F, RT, PF, true>;
+      static unsigned attr_mask = 0;
+      if (!(attr_mask & (1u << dev))) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) != cudaSuccess) { wv_set_error("gemv (tma): cannot raise the shared-memory limit"); return WV_ECUDA; }
+        attr_mask |= 1u << dev;
+      }
+      TmaExt ext{};
+      ext.grp.n = nb;
+      for (int i = 0; i < nb; i++) {
+        const int nrows = nb == 1 ? re - rb_ : bl[i].rows;
+        ext.grp.rows[i] = bl[i].rows;
+        ext.grp.rows_base[i] = nrows / grid;
+        ext.grp.rows_rem[i] = nrows % grid;
+        ext.grp.plane[i][0] = bl[i].lo; ext.grp.plane[i][1] = bl[i].hi; ext.grp.plane[i][2] = bl[i].p0; ext.grp.plane[i][3] = bl[i].p1; ext.grp.plane[i][4] = bl[i].km;
+        ext.grp.y[i] = dys[i];
+      }
+      if (wv_cur_peers) { if (batch != 1 || nb != 1) return WV_ESHAPE; ext.peers = *wv_cur_peers; }
+      e = launch_pdl(kern, dim3(grid, batch), dim3(TMA_THREADS), smem, st, b, xq, dx, dys[0], rb_, re, g, g_err_dev, ext);
+    } else {
+      return 1;
+    }
+  }
   if (e != cudaSuccess) { wv_set_error("gemv (tma) launch: %s", cudaGetErrorString(e)); return WV_ECUDA; }
   return WV_OK;
 }
