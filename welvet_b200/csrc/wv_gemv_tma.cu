@@ -109,7 +109,9 @@ __device__ __forceinline__ void load_frag_smem(FragT<F>& f, const LaneOff& a) {
   else if constexpr (BL == 2) { const uint2 v = lds64(a.lo); f.lo[0] = v.x; f.lo[1] = v.y; }
   else if constexpr (BL == 4) { const uint4 v = lds128(a.lo); f.lo[0] = v.x; f.lo[1] = v.y; f.lo[2] = v.z; f.lo[3] = v.w; }
   else {
-    const uint4 v = lds128(a.lo), u = lds128(a.lo + 16);
+    // a.lo is the chunk's 32 bytes, or their upper half for the lanes that read the halves in the
+    // opposite order (see the kernel): the other half is always at a.lo ^ 16
+    const uint4 v = lds128(a.lo), u = lds128(a.lo ^ 16u);
     f.lo[0] = v.x; f.lo[1] = v.y; f.lo[2] = v.z; f.lo[3] = v.w; f.lo[4] = u.x; f.lo[5] = u.y; f.lo[6] = u.z; f.lo[7] = u.w;
   }
   if constexpr (BH == 1) f.hi[0] = lds32(a.hi);
@@ -288,8 +290,21 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
           xfr[k] = make_float4(xp[WvLane<BL>::j_of(k, 0)], xp[WvLane<BL>::j_of(k, 1)], xp[WvLane<BL>::j_of(k, 2)], xp[WvLane<BL>::j_of(k, 3)]);
       }
     } else {
-      if (live) quantize_chunk<F>(xr, xc);
-      else {
+      if (live) {
+        quantize_chunk<F>(xr, xc);
+        if constexpr (BL == 8) {
+          const bool sw = lane & 4;
+#pragma unroll
+          for (int l = 0; l < 3; l++) {
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+              const unsigned a0 = xr.xw[8 * l + k], a1 = xr.xw[8 * l + k + 4];
+              xr.xw[8 * l + k] = sw ? a1 : a0;
+              xr.xw[8 * l + k + 4] = sw ? a0 : a1;
+            }
+          }
+        }
+      } else {
 #pragma unroll
         for (int t = 0; t < 24; t++) xr.xw[t] = 0u;
         xr.mt = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -331,7 +346,13 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   };
 
   const unsigned sbase = smem_u32(smem);
-  const LaneOff lo0 = lane_offsets<F>(g, rg * RT, live ? c : g.cpr - 1, b.group);
+  LaneOff lo0 = lane_offsets<F>(g, rg * RT, live ? c : g.cpr - 1, b.group);
+  if constexpr (BL == 8) {
+    // 8-bit codes: a lane's chunk is 32 bytes, so the 16-byte loads of lanes i and i+4 of a quarter
+    // warp would fall into the same banks. Every second group of four lanes reads the two halves
+    // in the opposite order and keeps its activation words swapped to match.
+    if (lane & 4) lo0.lo ^= 16u;
+  }
   // Fetch the fragments of tile t from the ring into registers, then hand the stage back.
   // stage index and phase parity of the tile being fetched, advanced incrementally (no divisions
   // in the loop)
