@@ -136,8 +136,13 @@ __device__ __forceinline__ void mma_quantize_slot(unsigned slot) {
   }
 #pragma unroll
   for (int l = 0; l < 3; l++) {
-    sts128(slot + 32u * l, D[l][0], D[l][1], D[l][2], D[l][3]);
-    sts128(slot + 32u * l + 16u, D[l][4], D[l][5], D[l][6], D[l][7]);
+    if constexpr (BL == 8) {   // a lane of the 8-bit A operand holds groups p and p + 4 (see load_a): same pairing here
+      sts128(slot + 32u * l, D[l][0], D[l][4], D[l][1], D[l][5]);
+      sts128(slot + 32u * l + 16u, D[l][2], D[l][6], D[l][3], D[l][7]);
+    } else {
+      sts128(slot + 32u * l, D[l][0], D[l][1], D[l][2], D[l][3]);
+      sts128(slot + 32u * l + 16u, D[l][4], D[l][5], D[l][6], D[l][7]);
+    }
   }
   if constexpr (MmaCfg<F>::INT_MID)
     sts128(slot + MMA_SLOT_K, (unsigned)(-fi.mid * sl[0]), (unsigned)(-fi.mid * sl[1]), (unsigned)(-fi.mid * sl[2]), (unsigned)(-fi.mid * 32));
@@ -265,7 +270,7 @@ gemv_mma_kernel(const WvDevBlob b, const float* __restrict__ xf, float* __restri
   const unsigned maskA = lane < 16 ? 0xffffffffu : 0u, maskB = ~maskA;
   // A operand: this lane's word inside a chunk's lo / hi data and the shifts that bring its two
   // code groups (2p, 2p+1) down to bit 0
-  const unsigned lo_lane = BL == 8 ? p * 8u : (BL == 4 ? p * 4u : (BL == 2 ? (p >> 1) * 4u : 0u));
+  const unsigned lo_lane = BL >= 4 ? p * 4u : (BL == 2 ? (p >> 1) * 4u : 0u);
   const int sh_lo = BL == 2 ? (p & 1) * 4 : (BL == 1 ? 2 * p : 0);
   const int sh_hi = 2 * p;
   constexpr unsigned MASK = 0x01010101u * ((1u << (BL & 7)) - 1u);
@@ -277,8 +282,11 @@ gemv_mma_kernel(const WvDevBlob b, const float* __restrict__ xf, float* __restri
   auto ldf = [&](unsigned o) { return *reinterpret_cast<const float*>(smem + o); };
   auto load_a = [&](unsigned lo_o, unsigned hi_o, unsigned& q0, unsigned& q1) {
     if constexpr (BL == 8) {
-      const uint2 w = ld64(lo_o);
-      q0 = SIGNED_A ? w.x ^ 0x80808080u : w.x; q1 = SIGNED_A ? w.y ^ 0x80808080u : w.y;
+      // words p and p + 4 of the chunk's eight: the second sits in the neighbouring 16-byte unit, which the
+      // swizzle puts at the address with bit 4 flipped. Two 4-byte loads whose eight rows hit eight different
+      // units, where one 8-byte load of words 2p, 2p + 1 would put rows g and g ^ 1 on the same banks.
+      const unsigned w0 = ld32(lo_o), w1 = ld32(lo_o ^ 16u);
+      q0 = SIGNED_A ? w0 ^ 0x80808080u : w0; q1 = SIGNED_A ? w1 ^ 0x80808080u : w1;
     } else if constexpr (SIGNED_A) {   // 4-bit: signed code * 16 in each byte
       const unsigned w = ld32(lo_o);
       q0 = ((w << 4) & 0xF0F0F0F0u) ^ 0x80808080u; q1 = (w & 0xF0F0F0F0u) ^ 0x80808080u;
