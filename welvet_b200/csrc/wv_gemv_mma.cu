@@ -582,8 +582,8 @@ static int launch_mma(const WvDevBlob& b, const float* dx, float* dy, int batch,
     }
     e = launch_pdl(kern, dim3(grid, batch), dim3(MMA_THREADS), smem, st, b, dx, dy, rb_, g, wv_tma_err_ptr(),
                    maps.m[0], maps.m[1], maps.m[2], maps.m[3], MmaNoPeers{});
-  } else if constexpr (PW != 4) {
-    return 1;   // the peer-storing variant exists for the default pairs-per-warp only
+  } else if constexpr (PW != 4 && !(PW == 2 && F == WV_Q8_0)) {
+    return 1;   // the peer-storing variant exists for the default configurations only
   } else {
     if (batch != 1) return WV_ESHAPE;
     auto kern = gemv_mma_kernel<F, PW, NSEG, true>;
