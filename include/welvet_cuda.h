@@ -160,15 +160,6 @@ int wv_gather_read(const void* dptr, size_t offset_bytes, void* host, size_t byt
  * device failures through the error of the synchronous call (webgpu/affine_cache.go:439-443). */
 int wv_device_status(void);
 
-/* Experiment hook: override rows-per-warp / column split / prefetch depth / grid size of the
- * chunked GEMV (0 = built-in choice). Not part of the reference surface. */
-void wv_set_tuning(int rows_per_warp, int col_split, int depth, int grid);
-/* Same for the bulk-copy-fed kernels: rows per row group per tile (1, 2, 4, 8; 11-14 without register
- * prefetch) or 21 / 22 / 24 to route the formats with one parameter group per 32 weights through the
- * tensor-pipe kernel; ring depth cap in the low two digits of `stages`, tiles issued ahead of the
- * activation loads in the hundreds. */
-void wv_set_tma_tuning(int rows_per_group, int stages);
-
 #ifdef __cplusplus
 }
 #endif

@@ -218,3 +218,17 @@ def argmax(logits: np.ndarray) -> int:
     """sampling.ArgMax (model/sampling/argmax.go:4-18)."""
     v = np.ascontiguousarray(logits, np.float32).reshape(-1)
     return int(lib().wvo_argmax(v.ctypes.data_as(C.c_void_p), C.c_int64(v.size)))
+
+
+# core.ActivationType (core/layer.go:91-98)
+ACTIVATIONS = {"Linear": -1, "ReLU": 0, "SiLU": 1, "GELU": 2, "Tanh": 3, "Sigmoid": 4, "LeakyReLU": 5, "ReLU2": 6}
+
+
+def activate(v: np.ndarray, act: int) -> np.ndarray:
+    """core.Activate (core/activate.go:6-38) element by element in f64; unknown values of `act`
+    return the input unchanged, as the reference's default arm does."""
+    L = lib()
+    L.wvo_activate.restype = C.c_double
+    L.wvo_activate.argtypes = [C.c_double, C.c_int, C.POINTER(C.c_int)]
+    a = np.asarray(v, np.float64).reshape(-1)
+    return np.array([L.wvo_activate(float(t), int(act), None) for t in a], np.float64).reshape(np.shape(v))

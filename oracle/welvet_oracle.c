@@ -1293,3 +1293,22 @@ int wvo_argmax(const float *logits, int64_t n) {
   }
   return (int)max_idx;
 }
+
+/* ---------- pointwise activation (core/activate.go:6-38, values core/layer.go:91-98) ----------
+ * core.Activate in float64. An unknown value comes back unchanged, as in the reference's
+ * default arm; *known (may be NULL) reports whether the value is one of the eight. */
+double wvo_activate(double x, int act, int *known) {
+  if (known) *known = 1;
+  switch (act) {
+  case -1: return x;                                   /* ActivationLinear */
+  case 0: return x < 0 ? 0.0 : x;                      /* ActivationReLU */
+  case 6: return x < 0 ? 0.0 : x * x;                  /* ActivationReLU2 */
+  case 5: return x < 0 ? 0.01 * x : x;                 /* ActivationLeakyReLU */
+  case 1: return x / (1 + exp(-x));                    /* ActivationSilu */
+  case 2: return 0.5 * x * (1 + tanh(sqrt(2 / M_PI) * (x + 0.044715 * x * x * x)));  /* ActivationGELU */
+  case 3: return tanh(x);                              /* ActivationTanh */
+  case 4: return 1 / (1 + exp(-x));                    /* ActivationSigmoid */
+  }
+  if (known) *known = 0;
+  return x;
+}

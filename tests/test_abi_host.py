@@ -139,3 +139,25 @@ def test_row_shard_bookkeeping_two_ranks_gloo(tmp_path):
                         "--master-addr", "127.0.0.1", "--master-port", "29531", str(script)],
                        env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stderr[-2000:]
+
+
+def test_activation_values_match_the_reference_enum():
+    """core.ActivationType (core/layer.go:91-98): the integers are part of the call surface, so they
+    are pinned here as literals; the mirror's Activate must agree with the oracle's restatement of
+    core.Activate (core/activate.go:6-38) for every one of them."""
+    from welvet_b200 import dense
+    want = {"ActivationLinear": -1, "ActivationReLU": 0, "ActivationSilu": 1, "ActivationGELU": 2,
+            "ActivationTanh": 3, "ActivationSigmoid": 4, "ActivationLeakyReLU": 5, "ActivationReLU2": 6}
+    for name, val in want.items():
+        assert getattr(dense, name) == val, name
+    assert sorted(O.ACTIVATIONS.values()) == sorted(want.values())
+    hpp = open(os.path.join(ROOT, "welvet_b200", "host", "welvet.hpp")).read()
+    body = re.search(r"enum ActivationType : int \{(.*?)\};", hpp, re.S).group(1)
+    got = {k: int(v) for k, v in re.findall(r"(Activation\w+)\s*=\s*(-?\d+)", body)}
+    assert got == want
+    v = np.array([-30.0, -2.5, -1.0, -1e-3, 0.0, 1e-3, 0.7, 1.0, 2.5, 30.0])
+    for act in want.values():
+        np.testing.assert_allclose(dense.Activate(v, act), O.activate(v, act), rtol=1e-15, atol=0)
+    with pytest.raises(_lib().WelvetError):
+        dense.Activate(v, 7)
+    np.testing.assert_array_equal(O.activate(v, 7), v)   # the reference's default arm: unchanged

@@ -4,6 +4,7 @@ the C restatement with the second numpy restatement, internal consistency of the
 SIMD-path arithmetic, the wire round trip, and the committed golden fixtures."""
 import os
 import struct
+import sys
 
 import numpy as np
 import pytest
@@ -172,3 +173,43 @@ def test_argmax_restatement():
     assert O.argmax(np.zeros(0, np.float32)) == 0
     v = np.random.default_rng(0).normal(0, 1, 5000).astype(np.float32)
     assert O.argmax(v) == int(np.argmax(v))
+
+
+def test_oracle_against_reference_dump():
+    """Pins the oracle against the reference itself when tests/golden/ref_go_dump.bin is present: the
+    output of oracle/ref_dump/main.go (the reference's own quant.Pack / Unpack / MatVec and
+    dense.MatVecPackedBlob run with Go on the inputs of tests/golden/make_ref_inputs.py). Packed
+    bytes, scales, mins and dequantised weights must agree bit for bit, the scalar MatVec bit for bit
+    (same f32 order), the SIMD path to 1e-6 relative (f64 accumulation, thread split may differ)."""
+    import struct
+    gold = os.path.join(os.path.dirname(__file__), "golden")
+    dump = os.path.join(gold, "ref_go_dump.bin")
+    if not os.path.exists(dump):
+        pytest.skip("parity unpinned: reference fixtures absent (no Go toolchain here; see oracle/ref_dump/main.go)")
+    sys.path.insert(0, gold)
+    import make_ref_inputs
+    data = open(dump, "rb").read()
+    (n,) = struct.unpack_from("<I", data, 0)
+    off = 4
+    cs = list(make_ref_inputs.cases())
+    assert n == len(cs)
+    for f, rows, cols, w, x in cs:
+        fmt, r, c, bw, nraw, ns, nm, has_simd = struct.unpack_from("<8I", data, off)
+        off += 32
+        assert (fmt, r, c) == (f, rows, cols)
+        raw = np.frombuffer(data, np.uint8, nraw, off); off += nraw
+        scales = np.frombuffer(data, "<f4", ns, off); off += 4 * ns
+        mins = np.frombuffer(data, "<f4", nm, off); off += 4 * nm
+        un = np.frombuffer(data, "<f4", rows * cols, off); off += 4 * rows * cols
+        y_scalar = np.frombuffer(data, "<f4", rows, off); off += 4 * rows
+        y_simd = np.frombuffer(data, "<f4", rows, off); off += 4 * rows
+        ob = O.pack(f, w, rows, cols, 64 if f == O.FMT["AffinePacked"] else 0)
+        tag = f"{O.FORMATS[f]} {rows}x{cols}"
+        assert np.array_equal(ob.raw, raw), tag + ": Raw"
+        assert np.array_equal(ob.scales.view(np.uint32), scales.view(np.uint32)), tag + ": Scales"
+        assert np.array_equal(ob.mins.view(np.uint32), mins.view(np.uint32)), tag + ": Mins"
+        assert np.array_equal(O.unpack(ob).view(np.uint32), un.view(np.uint32)), tag + ": Unpack"
+        assert np.array_equal(O.matvec(ob, x).view(np.uint32), y_scalar.view(np.uint32)), tag + ": MatVec"
+        if has_simd:
+            np.testing.assert_allclose(O.matvec_simd(ob, x, 1), y_simd, rtol=1e-6, atol=1e-7, err_msg=tag + ": SIMD path")
+    assert off == len(data)

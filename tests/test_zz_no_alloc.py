@@ -70,3 +70,43 @@ def test_static_scratch_entry_rejects_what_it_cannot_do(wv):
     assert L.wv_matvec_dev_static(0x2B0002, x.data_ptr(), y.data_ptr(), 512, rows, None) == _lib.WV_ESHAPE
     L.wv_blob_evict(0x2B0002)
     assert L.wv_matvec_dev_static(0x2B0003, x.data_ptr(), y.data_ptr(), 1024, rows, None) == _lib.WV_ENOTFOUND
+
+
+def test_static_scratch_entry_at_its_maximum_width_from_another_thread_without_allocating(wv):
+    """The widest shape the fixed array takes (32768 columns: the whole array and the kernel's largest
+    shared-memory record), called from a host thread that has never touched CUDA (such a thread starts
+    with device 0 current, whatever device the library is bound to), with the device's free memory
+    compared before and after a warmed call: the entry must not allocate."""
+    import threading
+    import torch
+    from welvet_b200 import _lib
+    L = _lib.lib()
+    rows, cols = 37, 32768
+    w, x = make_w(79, rows, cols)
+    ob = O.pack("Q4_K", w, rows, cols)
+    key = 0x2C0001
+    _lib.check(L.wv_blob_upload(key, ob.format, 1, rows, cols, 0, ob.raw.ctypes.data, ob.raw.size, None, 0, None, 0))
+    try:
+        dx = torch.from_numpy(x).cuda()
+        y = torch.full((rows,), float("nan"), device="cuda")
+        _lib.check(L.wv_matvec_dev_static(key, dx.data_ptr(), y.data_ptr(), cols, rows, None))   # first call: set-up
+        torch.cuda.synchronize()
+        result = {}
+
+        def worker():
+            free0, _ = torch.cuda.mem_get_info()
+            result["rc"] = L.wv_matvec_dev_static(key, dx.data_ptr(), y.data_ptr(), cols, rows, None)
+            torch.cuda.synchronize()
+            free1, _ = torch.cuda.mem_get_info()
+            result["delta"] = free0 - free1
+        t = threading.Thread(target=worker)
+        t.start()
+        t.join()
+        assert result["rc"] == 0, L.wv_last_error()
+        assert result["delta"] == 0, f"free device memory changed by {result['delta']} bytes across the call"
+        assert L.wv_device_status() == 0
+        den = O.sum_abs_wx(ob, x)
+        ref = O.matvec_simd(ob, x, 1)
+        assert np.all(np.abs(y.cpu().numpy().astype(np.float64) - ref) <= TOL * den + 1e-30)
+    finally:
+        L.wv_blob_evict(key)

@@ -17,9 +17,12 @@ SYMBOLS = [
     "wv_blob_upload", "wv_blob_upload_wire", "wv_blob_upload_shard", "wv_shard_range",
     "wv_blob_has", "wv_blob_evict", "wv_cache_clear", "wv_cache_bytes", "wv_cache_set_limit",
     "wv_blob_info", "wv_matvec", "wv_matvec_dev", "wv_unpack", "wv_unpack_dev",
-    "wv_pack_sizes", "wv_pack", "wv_pack_upload_dev", "wv_set_tuning", "wv_set_tma_tuning", "wv_device_status", "wv_matvec_dev_static",
+    "wv_pack_sizes", "wv_pack", "wv_pack_upload_dev", "wv_device_status", "wv_matvec_dev_static",
     "wv_argmax_dev", "wv_argmax", "wv_matvec_dev_multi", "wv_matvec_dev_gather", "wv_gather_alloc", "wv_gather_open", "wv_gather_close", "wv_gather_free", "wv_gather_read", "wv_gather_signal", "wv_gather_wait",
 ]
+
+# Development hooks (csrc/wv_dev_hooks.h): exported for tests and tuning runs, not part of the public header.
+DEV_HOOKS = ["wv_set_tuning", "wv_set_tma_tuning"]
 
 WV_OK, WV_ESHAPE, WV_EFORMAT, WV_ENOMEM, WV_ECUDA, WV_ETIMEOUT, WV_ENOTFOUND, WV_EINIT, WV_EARG = (
     0, -1, -2, -3, -4, -5, -6, -7, -8)

@@ -89,6 +89,13 @@ static int ensure_init() {
   return WV_OK;
 }
 
+// For entry points implemented in other files: the library's device becomes current on the calling
+// thread; returns its index, or WV_EINIT.
+int wv_api_bind_device() {
+  const int rc = ensure_init();
+  return rc ? rc : g_device;
+}
+
 // ---------------------------------------------------------------- sizes
 struct Sizes { size_t nraw, ns, nm; int group; long long npad; };
 
@@ -327,21 +334,31 @@ extern "C" int wv_blob_has(uint64_t key) {
   std::lock_guard<std::mutex> lk(g_mu);
   return g_cache.count(key) ? 1 : 0;
 }
+// Eviction takes the entry out of the map under the lock and frees it outside: the device-wide
+// synchronisation (kernels still reading the blob) and cudaFree must not stall concurrent lookups.
 extern "C" int wv_blob_evict(uint64_t key) {
-  std::lock_guard<std::mutex> lk(g_mu);
-  auto it = g_cache.find(key);
-  if (it == g_cache.end()) { wv_set_error("wv_blob_evict: key %llu not resident", (unsigned long long)key); return WV_ENOTFOUND; }
-  if (g_device >= 0) { cudaSetDevice(g_device); cudaDeviceSynchronize(); cudaFree(it->second.mem); }
-  g_cache_bytes -= it->second.dev_bytes;
-  g_cache.erase(it);
+  void* mem = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_cache.find(key);
+    if (it == g_cache.end()) { wv_set_error("wv_blob_evict: key %llu not resident", (unsigned long long)key); return WV_ENOTFOUND; }
+    mem = it->second.mem;
+    g_cache_bytes -= it->second.dev_bytes;
+    g_cache.erase(it);
+  }
+  if (g_device >= 0) { cudaSetDevice(g_device); cudaDeviceSynchronize(); cudaFree(mem); }
   return WV_OK;
 }
 extern "C" void wv_cache_clear(void) {
-  std::lock_guard<std::mutex> lk(g_mu);
+  std::vector<void*> mems;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    for (auto& kv : g_cache) mems.push_back(kv.second.mem);
+    g_cache.clear();
+    g_cache_bytes = 0;
+  }
   if (g_device >= 0) { cudaSetDevice(g_device); cudaDeviceSynchronize(); }
-  for (auto& kv : g_cache) cudaFree(kv.second.mem);
-  g_cache.clear();
-  g_cache_bytes = 0;
+  for (void* m : mems) cudaFree(m);
 }
 extern "C" uint64_t wv_cache_bytes(void) { std::lock_guard<std::mutex> lk(g_mu); return g_cache_bytes; }
 extern "C" void wv_cache_set_limit(uint64_t bytes) { std::lock_guard<std::mutex> lk(g_mu); g_cache_limit = bytes; }

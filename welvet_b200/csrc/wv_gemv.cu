@@ -14,6 +14,9 @@
 //     reference's own factorisation sc*sum(q*x) + mn*sum(x) (simd/dot_k.go:44-53);
 //   * warp-shuffle reduction, one store per row.
 #include "wv_gemv_common.cuh"
+#include "wv_dev_hooks.h"
+#include <cstdlib>
+#include <mutex>
 
 #ifndef WV_GEMV_THREADS
 #define WV_GEMV_THREADS 512
@@ -412,6 +415,7 @@ extern "C" void wv_set_tuning(int r, int s, int d, int grid) { g_tune_r = r; g_t
 // reused only after the ring wraps, i.e. after (arena / slot) further calls.
 static uint4* g_xq_arena = nullptr;
 static size_t g_xq_bytes = 0, g_xq_head = 0;
+static std::mutex g_xq_mu;   // host threads may launch concurrently: the ring head moves under a lock
 int wv_gemv_scratch_init(size_t bytes) {
   if (g_xq_arena) return WV_OK;
   if (cudaMalloc(&g_xq_arena, bytes) != cudaSuccess) { cudaGetLastError(); return WV_ENOMEM; }
@@ -420,6 +424,7 @@ int wv_gemv_scratch_init(size_t bytes) {
 }
 uint4* wv_scratch_take(size_t bytes) {
   bytes = (bytes + 255) & ~(size_t)255;
+  std::lock_guard<std::mutex> lk(g_xq_mu);
   if (!g_xq_arena || bytes > g_xq_bytes) return nullptr;
   if (g_xq_head + bytes > g_xq_bytes) g_xq_head = 0;
   uint4* p = reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(g_xq_arena) + g_xq_head);
@@ -582,13 +587,13 @@ __global__ void gather_signal_kernel(const WvFlagPeers p) {
   }
 }
 // One thread per rank polls its word until it reaches this rank's new wait number; bounded.
-__global__ void gather_wait_kernel(unsigned* flags, int n, int* err) {
+__global__ void gather_wait_kernel(unsigned* flags, int n, int* err, int max_polls) {
   __shared__ unsigned s_epoch;
   if (threadIdx.x == 0) s_epoch = ++flags[n + 1];               // word n + 1: steps waited for by this rank
   __syncthreads();
   if ((int)threadIdx.x < n) {
     bool ok = false;
-    for (int i = 0; i < (1 << 17) && !ok; i++) {
+    for (int i = 0; i < max_polls && !ok; i++) {
       unsigned v;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + threadIdx.x) : "memory");
       ok = (int)(v - s_epoch) >= 0;
@@ -606,7 +611,15 @@ int wv_launch_gather_signal(unsigned* const* flags_all, int world, int rank, cud
 }
 int* wv_tma_err_ptr();
 int wv_launch_gather_wait(unsigned* flags_own, int world, cudaStream_t st) {
-  gather_wait_kernel<<<1, 32, 0, st>>>(flags_own, world, wv_tma_err_ptr());
+  // Bound of the wait: polls of about a quarter microsecond each. 250 ms by default (host jitter between ranks:
+  // a slow graph launch, a first-call attribute set), WELVET_CUDA_GATHER_WAIT_MS overrides it within [1, 2000].
+  static int max_polls = 0;
+  if (!max_polls) {
+    long ms = 250;
+    if (const char* e = getenv("WELVET_CUDA_GATHER_WAIT_MS")) { long v = atol(e); if (v >= 1 && v <= 2000) ms = v; }
+    max_polls = (int)(ms * 4000);
+  }
+  gather_wait_kernel<<<1, 32, 0, st>>>(flags_own, world, wv_tma_err_ptr(), max_polls);
   return cudaGetLastError() == cudaSuccess ? WV_OK : WV_ECUDA;
 }
 
@@ -672,9 +685,10 @@ static __device__ __align__(256) uint4 g_static_xq[9 * ((WV_STATIC_MAX_COLS >> 5
 static uint4* g_static_xq_addr[64] = {nullptr};
 
 int wv_api_get_blob(uint64_t key, WvDevBlob* out);  // wv_api.cu
+int wv_api_bind_device();                           // wv_api.cu: makes the library's device current, returns its index or an error
 
 template <int F>
-static int launch_static(const WvDevBlob& b, const float* dx, float* dy, uint4* xq, cudaStream_t st) {
+static int launch_static(const WvDevBlob& b, const float* dx, float* dy, uint4* xq, int dev, cudaStream_t st) {
   constexpr WvFmtInfo fi = wv_fmt_info(F);
   if constexpr (fi.table || fi.kind == WK_NONE) {
     wv_set_error("wv_matvec_dev_static: format %d uses no scratch and has no static variant", F);
@@ -684,7 +698,11 @@ static int launch_static(const WvDevBlob& b, const float* dx, float* dy, uint4* 
     const int cpr = b.cols >> 5, XS = cpr | 1;
     const size_t smem = (size_t)QCfg<F>::NREC * XS * 16 + (size_t)2 * (WV_GEMV_THREADS / 32) * R * 4 + 16;
     auto kern = gemv_idot_kernel<F, R, S, D>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return WV_ECUDA;
+    static unsigned long long attr_mask = 0;   // the attribute is set once per device, not per call
+    if (!(attr_mask & (1ull << dev))) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return WV_ECUDA;
+      attr_mask |= 1ull << dev;
+    }
     int rc = launch_xquant<fi.bits_lo>(dx, b.cols, 1, QCfg<F>::INT_MID ? fi.mid : 0, xq, st);
     if (rc) return rc;
     int grid = wv_sm_count();
@@ -700,6 +718,8 @@ static int launch_static(const WvDevBlob& b, const float* dx, float* dy, uint4* 
 // the address of the static scratch (cudaGetSymbolAddress with that device current); make that
 // first call before starting any stream capture.
 extern "C" int wv_matvec_dev_static(uint64_t key, const float* dx, float* dy, int in, int out, void* stream) {
+  const int dev = wv_api_bind_device();   // cudaSetDevice(bound device): a fresh host thread starts on device 0
+  if (dev < 0) return dev;
   if (!dx || !dy) { wv_set_error("wv_matvec_dev_static: null pointer"); return WV_EARG; }
   WvDevBlob b;
   int rc = wv_api_get_blob(key, &b);
@@ -710,8 +730,7 @@ extern "C" int wv_matvec_dev_static(uint64_t key, const float* dx, float* dy, in
     wv_set_error("wv_matvec_dev_static: cols=%d exceeds the static scratch maximum of %d", b.cols, WV_STATIC_MAX_COLS);
     return WV_ESHAPE;
   }
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { wv_set_error("wv_matvec_dev_static: bad device"); return WV_ECUDA; }
+  if (dev >= 64) { wv_set_error("wv_matvec_dev_static: bad device"); return WV_ECUDA; }
   if (!g_static_xq_addr[dev]) {
     void* p = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&p, g_static_xq);
@@ -721,7 +740,7 @@ extern "C" int wv_matvec_dev_static(uint64_t key, const float* dx, float* dy, in
   uint4* xq = g_static_xq_addr[dev];
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (b.format) {
-#define WV_F(f) case f: return launch_static<f>(b, dx, dy, xq, st);
+#define WV_F(f) case f: return launch_static<f>(b, dx, dy, xq, dev, st);
   WV_F(WV_Q8_0) WV_F(WV_Q4_0) WV_F(WV_Q4_1) WV_F(WV_Q5_0) WV_F(WV_Q5_1)
   WV_F(WV_Q2_K) WV_F(WV_Q3_K) WV_F(WV_Q4_K) WV_F(WV_Q5_K) WV_F(WV_Q6_K)
   WV_F(WV_IQ1_S) WV_F(WV_IQ2_XXS) WV_F(WV_IQ2_XS) WV_F(WV_IQ3_XXS) WV_F(WV_IQ3_S) WV_F(WV_IQ4_NL) WV_F(WV_IQ4_XS)

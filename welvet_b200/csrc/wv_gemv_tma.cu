@@ -15,6 +15,7 @@
 //   * all waits on mbarriers are bounded: when a wait runs out the CTA records an error code,
 //     stops issuing copies, drains the ones in flight (bounded again) and returns.
 #include "wv_gemv_common.cuh"
+#include "wv_dev_hooks.h"
 #include "wv_tma_common.cuh"
 
 #ifndef TMA_CONSUMER_WARPS

@@ -14,8 +14,17 @@ from ._lib import WelvetError, check, lib
 
 # core.Backend (core/layer.go:125-131) plus the new value.
 BackendCPUTiled, BackendSIMD, BackendWebGPU, BackendCUDA = 0, 1, 2, 3
-# core.ActivationType values used by Dense heads (core/activate.go)
-ActivationLinear, ActivationReLU, ActivationSigmoid, ActivationTanh = 0, 1, 2, 3
+# core.ActivationType (core/layer.go:91-98): the integer values are part of the call surface.
+ActivationLinear = -1
+ActivationReLU = 0
+ActivationSilu = 1
+ActivationGELU = 2
+ActivationTanh = 3
+ActivationSigmoid = 4
+ActivationLeakyReLU = 5
+ActivationReLU2 = 6
+_ACTIVATIONS = (ActivationLinear, ActivationReLU, ActivationSilu, ActivationGELU, ActivationTanh, ActivationSigmoid,
+                ActivationLeakyReLU, ActivationReLU2)
 
 
 @dataclass
@@ -51,14 +60,28 @@ def _dims(l: Layer, x: np.ndarray) -> Tuple[int, int, int]:
     return batch, in_, out
 
 
-def _activate(v: np.ndarray, act: int) -> np.ndarray:
+def Activate(v: np.ndarray, act: int) -> np.ndarray:
+    """core.Activate (core/activate.go:6-38) over an f64 array. The reference hands an unknown
+    activation value back unchanged; here it is an error, so that a layer built with integers
+    from another numbering cannot run silently as a linear one."""
+    v = np.asarray(v, np.float64)
+    if act == ActivationLinear:
+        return v
     if act == ActivationReLU:
-        return np.maximum(v, 0)
-    if act == ActivationSigmoid:
-        return 1.0 / (1.0 + np.exp(-v))
+        return np.where(v < 0, 0.0, v)
+    if act == ActivationReLU2:
+        return np.where(v < 0, 0.0, v * v)
+    if act == ActivationLeakyReLU:
+        return np.where(v < 0, 0.01 * v, v)
+    if act == ActivationSilu:
+        return v / (1.0 + np.exp(-v))
+    if act == ActivationGELU:
+        return 0.5 * v * (1.0 + np.tanh(np.sqrt(2.0 / np.pi) * (v + 0.044715 * v * v * v)))
     if act == ActivationTanh:
         return np.tanh(v)
-    return v
+    if act == ActivationSigmoid:
+        return 1.0 / (1.0 + np.exp(-v))
+    raise WelvetError(_lib.WV_EARG, f"dense: unknown activation {act}")
 
 
 def MatVecCUDA(s: weights.Store, x: np.ndarray, y: np.ndarray, batch: int, in_: int, out: int) -> None:
@@ -88,6 +111,8 @@ def ForwardCUDA(l: Layer, input: np.ndarray) -> Tuple[np.ndarray, np.ndarray]:
     the device, then bias + activation (applyBiasAct, dense.go:145-167). Linear / no bias
     aliases post to pre."""
     batch, in_, out = _dims(l, input)
+    if l.Activation not in _ACTIVATIONS:
+        raise WelvetError(_lib.WV_EARG, f"dense: unknown activation {l.Activation}")
     pre = np.empty((batch, out), input.dtype)
     y = np.empty(batch * out, np.float32)
     MatVecCUDA(l.Weights, np.asarray(input, np.float32), y, batch, in_, out)
@@ -99,7 +124,8 @@ def ForwardCUDA(l: Layer, input: np.ndarray) -> Tuple[np.ndarray, np.ndarray]:
     if bias is not None and len(bias):
         v[:, : len(bias)] += np.asarray(bias, np.float64)[:out]
         pre[...] = v
-    post = _activate(v, l.Activation).astype(input.dtype)
+    with np.errstate(over="ignore"):   # Activate(FromFloat64[T](v), act): v passes through T first (dense.go:163)
+        post = Activate(v.astype(input.dtype), l.Activation).astype(input.dtype)
     return pre, post
 
 

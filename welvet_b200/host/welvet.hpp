@@ -55,7 +55,27 @@ inline const char* BackendString(Backend b) {
   return "unknown";
 }
 enum DType : int { DTypeFloat32 = 1, DTypeFloat16 = 2, DTypeBFloat16 = 3 };  // the three FormatNone dtypes the backend streams
-enum ActivationType : int { ActivationLinear = 0, ActivationReLU = 1, ActivationSigmoid = 2, ActivationTanh = 3 };
+// core.ActivationType (core/layer.go:91-98): the integer values are part of the call surface.
+enum ActivationType : int {
+  ActivationLinear = -1, ActivationReLU = 0, ActivationSilu = 1, ActivationGELU = 2, ActivationTanh = 3,
+  ActivationSigmoid = 4, ActivationLeakyReLU = 5, ActivationReLU2 = 6
+};
+// core.Activate (core/activate.go:6-38) in f64. `ok` turns false for a value outside the enum: the
+// reference hands such a value back unchanged, this mirror reports it (dense::ForwardCUDA).
+inline double Activate(double x, ActivationType act, bool* ok = nullptr) {
+  switch (act) {
+  case ActivationLinear: return x;
+  case ActivationReLU: return x < 0 ? 0.0 : x;
+  case ActivationReLU2: return x < 0 ? 0.0 : x * x;
+  case ActivationLeakyReLU: return x < 0 ? 0.01 * x : x;
+  case ActivationSilu: return x / (1 + std::exp(-x));
+  case ActivationGELU: return 0.5 * x * (1 + std::tanh(std::sqrt(2 / 3.14159265358979323846) * (x + 0.044715 * x * x * x)));
+  case ActivationTanh: return std::tanh(x);
+  case ActivationSigmoid: return 1 / (1 + std::exp(-x));
+  }
+  if (ok) *ok = false;
+  return x;
+}
 struct ExecConfig { Backend Backend_ = BackendCUDA; bool MultiCore = true; int TileSize = 32; };  // core/layer.go:147-153
 
 template <typename T> struct Tensor {  // core.Tensor[T]: flat data + shape
@@ -338,6 +358,11 @@ std::tuple<TensorPtr<T>, TensorPtr<T>, Error> ForwardCUDA(const Layer* l, const 
   if (input->Shape[1] != in) return {nullptr, nullptr, errorf(WV_ESHAPE, "dense: input width != layer in")};
   if (l->Weights->Rows != out || l->Weights->Cols != in) return {nullptr, nullptr, errorf(WV_ESHAPE, "dense: weight shape != out x in")};
   if (input->Data.size() < (size_t)batch * in) return {nullptr, nullptr, errorf(WV_ESHAPE, "dense: input data short")};
+  {
+    bool known = true;
+    core::Activate(0.0, l->Activation, &known);
+    if (!known) return {nullptr, nullptr, errorf(WV_EARG, "dense: unknown activation " + std::to_string((int)l->Activation))};
+  }
   std::vector<float> xf(input->Data.begin(), input->Data.begin() + (size_t)batch * in), yf((size_t)batch * out);
   if (Error e = MatVecCUDA(l->Weights.get(), xf, yf, batch, in, out)) return {nullptr, nullptr, e};
   auto pre = core::NewTensor<T>(batch, out), post = core::NewTensor<T>(batch, out);
@@ -347,14 +372,7 @@ std::tuple<TensorPtr<T>, TensorPtr<T>, Error> ForwardCUDA(const Layer* l, const 
       double v = (double)yf[(size_t)bi * out + o];
       if ((size_t)o < bias.size()) v += bias[o];
       pre->Data[(size_t)bi * out + o] = (T)v;
-      double a = v;
-      switch (l->Activation) {
-      case core::ActivationReLU: a = v > 0 ? v : 0; break;
-      case core::ActivationSigmoid: a = 1.0 / (1.0 + std::exp(-v)); break;
-      case core::ActivationTanh: a = std::tanh(v); break;
-      default: break;
-      }
-      post->Data[(size_t)bi * out + o] = (T)a;
+      post->Data[(size_t)bi * out + o] = (T)core::Activate((double)(T)v, l->Activation);
     }
   }
   return {std::move(pre), std::move(post), Error{}};
