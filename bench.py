@@ -4,18 +4,18 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
 One step = one batch-1 GEMV for every format of the format sweep at 4096x14336 and at
-14336x4096 (Llama-3-8B FFN shapes), weights N(0, 0.02^2) seed 2 packed by the device packer
-(byte-identical to the reference packer), activations N(0, 1). `value` is GB/s of packed
-weight bytes (len(Raw) + 4 len(Scales) + 4 len(Mins)) with everything resident in HBM;
-one step streams ~1.36 GB of distinct weights, far more than L2, so no launch reads
-L2-resident weights. `e2e` is the same metric through the host-pointer plugin call
+14336x4096 (Llama-3-8B FFN shapes), weights N(0, 0.02^2) seed 2, activations N(0, 1) seed 1.
+`value` is GB/s of packed weight bytes (len(Raw) + 4 len(Scales) + 4 len(Mins)) with everything
+resident in HBM; one step streams ~1.36 GB of distinct weights, far more than L2, so no launch
+reads L2-resident weights. `e2e` is the same metric through the host-pointer plugin call
 (wv_matvec: host x in, host y out, copies inside the timed region).
 
-With N > 1 (launched by torch.distributed.run) every matrix is row-sharded across the ranks
-and the y slices are all-gathered over NCCL after each GEMV (strong scaling).
+With N > 1 (launched by torch.distributed.run) every matrix is row-sharded across the ranks and
+each rank's kernels store their rows into every rank's output vectors (strong scaling).
 
 --impl reference times the CPU restatement of the reference's SIMD path (oracle/) on the host
-cores: it is the reference arm, not the product.
+cores over the same sweep: it is the reference arm, not the product. Both arms print the same
+metric, unit and config.
 """
 from __future__ import annotations
 
@@ -33,6 +33,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+METRIC = "quant GEMV GB/s of packed weight bytes"
 SHAPES = [(4096, 14336), (14336, 4096)]
 # The format sweep: (name, quant.Format value, BlockWeights, FormatNone dtype)
 SWEEP = [("Q4_0", 2, 0, 1), ("Q4_1", 3, 0, 1), ("Q5_0", 4, 0, 1), ("Q5_1", 5, 0, 1), ("Q8_0", 1, 0, 1),
@@ -42,18 +43,25 @@ SWEEP = [("Q4_0", 2, 0, 1), ("Q4_1", 3, 0, 1), ("Q5_0", 4, 0, 1), ("Q5_1", 5, 0,
 # Measured per format but outside the timed step (named by the target, not by the sweep config).
 EXTRA = [("AffinePacked_g64", 20, 64, 1), ("BinaryPacked_g32", 19, 32, 1), ("none_f16", 0, 0, 2), ("none_bf16", 0, 0, 3), ("none_f32", 0, 0, 1)]
 NOMINAL_HBM_GBS = 8000.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
-# profiles/gemv_tma_gemv_mma_q4_0_q8_0_q4_k_full.md (4096x14336; the other shape reads the same within 0.1 %),
-# next to the algorithmic bytes of the same launches: one launch streams its blob exactly once.
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from ncu captures of single launches
+# (4096x14336), next to the algorithmic bytes of the same launches: one launch streams its blob once.
 NCU_DRAM_BYTES = {"Q4_0": 36792320, "Q8_0": 66262016, "Q4_K": 38627328}
 NCU_ALGO_BYTES = {"Q4_0": 36700160, "Q8_0": 66060288, "Q4_K": 38535168}
+MIN_TIMED_S = 0.25   # the timed region is lengthened to at least this by replaying the step
+
+
+def common_config(sweep):
+    """The workload description both arms print, word for word."""
+    return {"workload": "format_sweep_4096x14336+14336x4096", "formats": [f[0] for f in sweep], "batch": 1,
+            "weights": "N(0,0.02^2) seed 2", "activations": "N(0,1) seed 1",
+            "l2": "inputs larger than L2: one step streams 1365 MB of distinct packed weights (38 matrices, 9-66 MB each)"}
 
 
 def measured_hbm_peak():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json, burst copy)"
-    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+    return 6650.0, "fallback (6.65 TB/s)"
 
 
 class ClockSampler:
@@ -65,7 +73,7 @@ class ClockSampler:
         self.rows = []
         self.proc = None
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(index)],
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(index)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -101,27 +109,39 @@ def gen_weights(rows, cols):
     return np.random.default_rng(2).normal(0, 0.02, rows * cols).astype(np.float32)
 
 
+def gen_x(cols):
+    return np.random.default_rng(1).normal(0, 1, cols).astype(np.float32)
+
+
 # ------------------------------------------------------------------------------ reference arm
-def cpu_leg(steps, warmup, formats, shape, threads=0):
-    """Times the oracle's restatement of the reference SIMD path (dense.MatVecPackedBlob) on the
-    host cores for `formats` at `shape`; returns (GB/s of packed bytes, cores used, seconds per step)."""
+def cpu_leg(steps, warmup, formats, shapes, threads=0):
+    """Times the oracle's restatement of the reference SIMD path (dense.MatVecPackedBlob) on the host
+    cores for `formats` at `shapes`; returns (GB/s of packed bytes, cores used, seconds per step, bytes)."""
     import oracle as O
-    rows, cols = shape
-    w = gen_weights(rows, cols)
-    x = np.random.default_rng(1).normal(0, 1, cols).astype(np.float32)
-    y = np.zeros(rows, np.float32)
-    caches, total = [], 0
-    for name, fmt, bw, dt in formats:
-        ob = O.pack(fmt, w, rows, cols, bw, dt)
-        caches.append((O.SimdCache(ob), ob))
-        total += ob.packed_bytes
+    from concurrent.futures import ThreadPoolExecutor
+    O.lib()
+    work, total = [], 0
+    for rows, cols in shapes:
+        w = gen_weights(rows, cols)
+        x = gen_x(cols)
+        y = np.zeros(rows, np.float32)
+
+        def prepare(spec):
+            name, fmt, bw, dt = spec
+            ob = O.pack(fmt, w, rows, cols, bw, dt)
+            return O.SimdCache(ob), ob   # caches are built once, outside the timed loop, as in the reference
+        with ThreadPoolExecutor(max_workers=min(16, os.cpu_count() or 1)) as ex:   # packing only: the timed loop below is serial
+            for cache, ob in ex.map(prepare, formats):
+                work.append((cache, ob, x, y))
+                total += ob.packed_bytes
+        del w
     cores = 1
     for _ in range(warmup):
-        for c, _ in caches:
+        for c, _, x, y in work:
             cores = max(cores, c.matvec(x, y, threads))
     t0 = time.perf_counter()
     for _ in range(steps):
-        for c, _ in caches:
+        for c, _, x, y in work:
             c.matvec(x, y, threads)
     dt_s = (time.perf_counter() - t0) / max(steps, 1)
     return total / dt_s / 1e9, cores, dt_s, total
@@ -130,14 +150,14 @@ def cpu_leg(steps, warmup, formats, shape, threads=0):
 def run_reference(args, rank, world):
     if rank != 0:
         return
-    # Bounded sample of the sweep: every format family at 4096x14336, sized to finish in minutes.
-    sample = [f for f in SWEEP if f[0] in ("Q4_0", "Q8_0", "Q4_1", "Q5_1", "Q4_K", "Q6_K", "IQ3_S", "IQ4_NL", "TernaryPacked", "BinaryPacked_g128")]
-    gbs, cores, sec, total = cpu_leg(args.steps, max(args.warmup, 1), sample, SHAPES[0])
-    desc = f"{len(sample)} formats ({','.join(f[0] for f in sample)}) at {SHAPES[0][0]}x{SHAPES[0][1]}, {total/1e6:.0f} MB packed per step"
-    out = {"impl": "reference", "metric": "quant GEMV GB/s of packed weight bytes", "value": gbs, "unit": "GB/s",
+    sweep = [f for f in SWEEP if not args.formats or f[0] in args.formats.split(",")]
+    gbs, cores, sec, total = cpu_leg(args.steps, max(args.warmup, 1), sweep, SHAPES)
+    desc = (f"the whole sweep per step: {len(sweep)} formats at both shapes, {total/1e6:.0f} MB packed per step, "
+            f"SIMD-path caches prebuilt, {cores} host threads")
+    out = {"impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s",
            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f64 accumulate (reference SIMD path)",
-           "data": "synthetic", "config": {"workload": "format_sweep_4096x14336+14336x4096 (bounded sample: " + desc + ")"},
+           "data": "synthetic", "config": common_config(sweep),
            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": desc},
            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
            "gpu_launches": 0}
@@ -157,12 +177,47 @@ def emit(obj):
         os.write(_STDOUT_FD, line)
 
 
+def time_graph(torch, stream, graph, reps=5):
+    """Best of `reps` device times of one replay of `graph` (ms), CUDA events on the launching stream."""
+    best = 1e30
+    with torch.cuda.stream(stream):
+        graph.replay()
+        stream.synchronize()
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream); graph.replay(); b.record(stream)
+            stream.synchronize()
+            best = min(best, a.elapsed_time(b))
+    return best
+
+
+def parity_sample(torch, L, _lib, O, spec, w_host, x_host, rows, cols, key, y_dev, scratch):
+    """Parity beside a timed number: on three 64-row bands of the matrix the device's dequantised weights
+    (wv_unpack_dev) are compared bit for bit with the oracle's Unpack, and the GEMV output that was just
+    timed with the oracle's SIMD-path MatVec (max |y - y_ref| / sum|w x| over the rows). Bands are packed by
+    the oracle's own packer (rows are whole blocks at these shapes, so a band packs to the bytes it has
+    inside the full matrix)."""
+    name, fmt, bw, dt = spec
+    _lib.check(L.wv_unpack_dev(key, scratch.data_ptr(), None))
+    torch.cuda.synchronize()
+    y = y_dev.cpu().numpy()
+    exact, worst = True, 0.0
+    for r0 in (0, (rows // 2) & ~63, rows - 64):
+        ob = O.pack(fmt, w_host[r0 * cols:(r0 + 64) * cols], 64, cols, bw, dt)
+        want = torch.from_numpy(O.unpack(ob).view(np.int32)).cuda()
+        got = scratch[r0 * cols:(r0 + 64) * cols].view(torch.int32)
+        exact = exact and bool(torch.equal(want, got))
+        ref = O.matvec_simd(ob, x_host, 0).astype(np.float64)
+        den = O.sum_abs_wx(ob, x_host)
+        worst = max(worst, float(np.max(np.abs(y[r0:r0 + 64].astype(np.float64) - ref) / np.maximum(den, 1e-30))))
+    return exact, worst
+
+
 def decode_projections(torch, L, _lib, stream):
     """Time of the projection GEMVs of one decoded token for Llama-8B shapes in Q4_K, chained as in the
     model: 32 x [Q|K|V group, O, gate|up group, down] and the LM head followed by the greedy pick, all
-    in one CUDA graph. Norms, RoPE and attention are not part of this library yet and are left out,
-    so this is the GEMV share of a token, not a tokens/s claim for the whole model."""
-    import ctypes as C
+    in one CUDA graph. Norms, RoPE and attention are left out, so this is the GEMV share of a token,
+    not a tokens/s claim for the whole model."""
     fmt, hid, ffn, kv, vocab, layers = 8, 4096, 14336, 1024, 128256, 32   # Q4_K
     shapes = {"q": (hid, hid), "k": (kv, hid), "v": (kv, hid), "o": (hid, hid), "gate": (ffn, hid), "up": (ffn, hid), "down": (hid, ffn)}
     key = 0x40000
@@ -215,15 +270,7 @@ def decode_projections(torch, L, _lib, stream):
     g = torch.cuda.CUDAGraph()
     with torch.cuda.graph(g, stream=stream):
         token(torch.cuda.current_stream().cuda_stream)
-    best = 1e30
-    with torch.cuda.stream(stream):
-        g.replay()
-        stream.synchronize()
-        for _ in range(5):
-            a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(stream); g.replay(); b_.record(stream)
-            stream.synchronize()
-            best = min(best, a.elapsed_time(b_))
+    best = time_graph(torch, stream, g)
     del g
     for blk in blocks:
         for k in blk.values():
@@ -232,7 +279,7 @@ def decode_projections(torch, L, _lib, stream):
     return {"model": "Llama-8B shapes (32 blocks: Q|K|V, O, gate|up, down; LM head 128256x4096; greedy pick)", "format": "Q4_K",
             "launches_per_token": layers * 4 + 2, "packed_bytes_per_token": token_bytes, "ms_per_token": round(best, 4),
             "gbs": round(token_bytes / best / 1e6, 1), "tokens_per_s_gemv_only": round(1e3 / best, 1),
-            "note": "projection GEMVs and the pick only; norms, RoPE and attention are outside this library and not timed"}
+            "note": "projection GEMVs and the pick only; norms, RoPE and attention are not timed"}
 
 
 def main():
@@ -248,6 +295,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="welvet_b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the per-format parity fields")
     ap.add_argument("--formats", default="", help="comma list: restrict the sweep (for profiler captures)")
     ap.add_argument("--quick", action="store_true", help="skip the per-format table, the e2e and the CPU legs (profiler captures)")
     args = ap.parse_args()
@@ -273,24 +321,27 @@ def main():
     stream = torch.cuda.Stream()
 
     # ---- build the sweep on the device (device packer == reference packer, byte for byte)
-    jobs = []          # (name, key, rows_local, cols, rows, wire_bytes_full, y_full, y_local_view)
+    jobs = []
     extra_jobs = []
-    xs = {}
+    xs, xh, wh = {}, {}, {}
     nkey = 0x10000
     for rows, cols in SHAPES:
-        w = torch.from_numpy(gen_weights(rows, cols)).cuda()
-        xs[cols] = torch.from_numpy(np.random.default_rng(1).normal(0, 1, cols).astype(np.float32)).cuda()
+        wh[cols] = gen_weights(rows, cols)
+        w = torch.from_numpy(wh[cols]).cuda()
+        xh[cols] = gen_x(cols)
+        xs[cols] = torch.from_numpy(xh[cols]).cuda()
         lo, hi = C.c_int(), C.c_int()
         _lib.check(L.wv_shard_range(rows, rank, world, C.byref(lo), C.byref(hi)))
         r0, r1 = lo.value, hi.value
         for group, lst in ((jobs, sweep), (extra_jobs, extra if world == 1 else [])):
-            for name, fmt, bw, dt in lst:
+            for spec in lst:
+                name, fmt, bw, dt = spec
                 nkey += 1
                 _lib.check(L.wv_pack_upload_dev(nkey, fmt, dt, bw, w.data_ptr() + r0 * cols * 4, r1 - r0, cols, None))
                 wb = C.c_uint64()
                 _lib.check(L.wv_blob_info(nkey, None, None, C.byref(wb), None, None))
                 y = torch.zeros(rows, device="cuda")
-                group.append(dict(name=name, key=nkey, rows=rows, cols=cols, r0=r0, r1=r1, bytes=int(wb.value), y=y))
+                group.append(dict(name=name, spec=spec, key=nkey, rows=rows, cols=cols, r0=r0, r1=r1, bytes=int(wb.value), y=y))
         del w
     torch.cuda.synchronize()
 
@@ -327,32 +378,34 @@ def main():
             _lib.check(L.wv_gather_signal(f_all, world, rank, st))
             _lib.check(L.wv_gather_wait(gflags.own, world, st))
 
-    def step_plain():
-        for j in jobs:
+    with torch.cuda.stream(stream):
+        for j in jobs:                     # first call per kernel sets its attributes (not capturable)
             launch(j, stream.cuda_stream)
         step_end(stream.cuda_stream)
-
-    with torch.cuda.stream(stream):
-        step_plain()                      # first call per kernel sets its attributes (not capturable)
     stream.synchronize()
-    # One CUDA graph per step: the 38 GEMV launches and nothing else, at every N.
+    # One CUDA graph per step: the 38 GEMV launches (and, sharded, the two flag kernels), at every N.
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph, stream=stream):
         cur = torch.cuda.current_stream().cuda_stream
         for j in jobs:
             launch(j, cur)
         step_end(cur)
-    launch_mode = "cuda graph"
 
-    def run_step():
-        if graph is not None:
-            graph.replay()
-        else:
-            step_plain()
-
+    # The step graph is replayed R times per step so that the timed region lasts at least MIN_TIMED_S
+    # (20 steps of 0.3 ms would be 6 ms: too short for a clock sample); the time is divided by K * R.
     with torch.cuda.stream(stream):
         for _ in range(args.warmup):
-            run_step()
+            graph.replay()
+        stream.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream); graph.replay(); b.record(stream)
+        stream.synchronize()
+        probe_ms = a.elapsed_time(b)
+    reps = max(1, int(np.ceil(MIN_TIMED_S * 1e3 / max(probe_ms * args.steps, 1e-3))))
+    if world > 1:
+        t = torch.tensor([float(reps)], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        reps = int(t.item())
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
@@ -361,8 +414,8 @@ def main():
     torch.cuda.synchronize()
     with torch.cuda.stream(stream):
         e0.record(stream)
-        for _ in range(args.steps):
-            run_step()
+        for _ in range(args.steps * reps):
+            graph.replay()
         e1.record(stream)
     torch.cuda.synchronize()
     if world > 1:
@@ -373,7 +426,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     clocks = sampler.stop() if sampler else None
-    ms_step = ms / args.steps
+    ms_step = ms / (args.steps * reps)
     full_bytes = sum(j["bytes"] for j in jobs)
     if world > 1:
         t = torch.tensor([float(full_bytes)], device="cuda")
@@ -384,13 +437,13 @@ def main():
 
     gather_ok = None
     if world > 1:
-        # the gathered vectors must equal the unsharded product's: checked on two jobs, on every rank
+        # the gathered vectors must equal the unsharded product's, bit for bit: every job, on every rank
         torch.cuda.synchronize()
         dist.barrier()
         ok = True
-        for j in (jobs[0], jobs[-1]):
-            w = torch.from_numpy(gen_weights(j["rows"], j["cols"])).cuda()
-            spec = next(f for f in sweep if f[0] == j["name"])
+        for j in jobs:
+            w = torch.from_numpy(wh[j["cols"]]).cuda()
+            spec = j["spec"]
             _lib.check(L.wv_pack_upload_dev(0x7FFF01, spec[1], spec[3], spec[2], w.data_ptr(), j["rows"], j["cols"], None))
             ref = torch.zeros(j["rows"], device="cuda")
             _lib.check(L.wv_matvec_dev(0x7FFF01, xs[j["cols"]].data_ptr(), ref.data_ptr(), 1, j["cols"], j["rows"], None))
@@ -418,18 +471,25 @@ def main():
 
     # ---- per-format kernel times, measured live: a CUDA graph of back-to-back launches of the one
     # kernel, rotating over K device copies of the blob (K * bytes >= 300 MB, more than twice L2) so
-    # that no launch reads L2-resident weights; CUDA events on the launching stream.
+    # that no launch reads L2-resident weights; CUDA events on the launching stream. Beside each time:
+    # the parity of that very blob and output against the oracle (dequant bit-exact, max relative error).
     peak, peak_src = measured_hbm_peak()
     per = []
-    last_cols, w = None, None
     if world == 1 and not args.quick:
+        O = None
+        scratch = None
+        if not args.no_parity:
+            import oracle as O
+            scratch = torch.empty(max(r * c for r, c in SHAPES), device="cuda")
+        last_cols, w = None, None
         for j in jobs + extra_jobs:
             K = max(2, min(32, int(np.ceil(300e6 / j["bytes"]))))
             keys = [j["key"]]
             rows, cols = j["rows"], j["cols"]
-            w = torch.from_numpy(gen_weights(rows, cols)).cuda() if cols != last_cols else w
+            if cols != last_cols:
+                w = torch.from_numpy(wh[cols]).cuda()
             last_cols = cols
-            spec = next(f for f in SWEEP + EXTRA if f[0] == j["name"])
+            spec = j["spec"]
             for k in range(1, K):
                 nkey += 1
                 _lib.check(L.wv_pack_upload_dev(nkey, spec[1], spec[3], spec[2], w.data_ptr(), rows, cols, None))
@@ -444,23 +504,20 @@ def main():
                 cur = torch.cuda.current_stream().cuda_stream
                 for i in range(n_l):
                     _lib.check(L.wv_matvec_dev(keys[i % K], xs[cols].data_ptr(), j["y"].data_ptr(), 1, cols, rows, cur))
-            with torch.cuda.stream(stream):
-                g.replay()
-                stream.synchronize()
-                best = 1e30
-                for _ in range(5):
-                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    a.record(stream); g.replay(); b.record(stream)
-                    stream.synchronize()
-                    best = min(best, a.elapsed_time(b) / n_l)
+            us = time_graph(torch, stream, g) / n_l * 1e3
             del g
             for k in keys[1:]:
                 L.wv_blob_evict(k)
-            us = best * 1e3
             gbs = j["bytes"] / us / 1e3
-            per.append({"format": j["name"], "rows": rows, "cols": cols, "packed_bytes": j["bytes"], "us": round(us, 2),
-                        "gbs": round(gbs, 1), "frac_measured_peak": round(gbs / peak, 3), "frac_8TBs": round(gbs / NOMINAL_HBM_GBS, 3),
-                        "copies_rotated": K, "in_step": j in jobs})
+            row = {"format": j["name"], "rows": rows, "cols": cols, "packed_bytes": j["bytes"], "us": round(us, 2),
+                   "gbs": round(gbs, 1), "frac_measured_peak": round(gbs / peak, 3), "frac_8TBs": round(gbs / NOMINAL_HBM_GBS, 3),
+                   "copies_rotated": K, "in_step": j in jobs}
+            if O is not None:
+                exact, rel = parity_sample(torch, L, _lib, O, spec, wh[cols], xh[cols], rows, cols, j["key"], j["y"], scratch)
+                row["dequant_bitexact"] = exact
+                row["max_rel"] = float(f"{rel:.3e}")
+            per.append(row)
+        del w, scratch
     # The step is 38 launches of one kernel family (a template instance per format); none of them
     # dominates, so the roofline is taken over the family: bytes per launch and launch duration
     # are the averages over the step's launches, each timed in its own same-kernel graph above.
@@ -474,7 +531,6 @@ def main():
                "slow": max(in_step, key=lambda p: p["us"]), "fast": max(in_step, key=lambda p: p["gbs"])}
 
     # ---- end to end through the host-pointer plugin call
-    xh = {c: xs[c].cpu().numpy() for c in xs}
     yh = {j["key"]: np.zeros(j["r1"] - j["r0"], np.float32) for j in jobs}
 
     def e2e_step():
@@ -482,50 +538,54 @@ def main():
             _lib.check(L.wv_matvec(j["key"], xh[j["cols"]].ctypes.data, yh[j["key"]].ctypes.data, 1, j["cols"], j["r1"] - j["r0"]))
     e2e_val = None
     if world == 1 and not args.quick:
-        for _ in range(2):
+        for _ in range(3):
             e2e_step()
+        n_e2e = max(args.steps, 20)
         t0 = time.perf_counter()
-        n_e2e = max(3, min(args.steps, 10))
         for _ in range(n_e2e):
             e2e_step()
         e2e_s = (time.perf_counter() - t0) / n_e2e
         e2e_val = full_bytes / e2e_s / 1e9
 
+    cfg = common_config(sweep)
     out = {
-        "metric": "quant GEMV GB/s of packed weight bytes (batch-1 format sweep)",
+        "metric": METRIC,
         "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "int8x4 dot (24-bit block-fixed-point activations) + f32 scale",
+        "dtype": "int8x4 dot (block-fixed-point activations) + f32 scale",
         "data": "synthetic",
-        "config": {"workload": "format_sweep_4096x14336+14336x4096", "formats": [f[0] for f in sweep], "batch": 1,
-                   "weights": "N(0,0.02^2) seed 2", "activations": "N(0,1) seed 1",
-                   "l2": "inputs larger than L2: one step streams %.0f MB of distinct packed weights" % (full_bytes / 1e6),
-                   "sharding": ("rows split evenly across ranks; each rank's GEMV kernels store their rows into every rank's y "
-                                "(peer mappings, no collective call); every step ends with on-device arrival flags; gathered y verified: %s" % gather_ok)
-                   if world > 1 else "single GPU",
-                   "launch": launch_mode,
-                   "pct_of_8TBs": round(100 * value / NOMINAL_HBM_GBS, 1)},
-        "gpu_launches": launches_per_step * args.steps,
+        "config": cfg,
+        "run": {"replays_per_step": reps, "timed_region_s": round(ms * 1e-3, 4), "launch": "cuda graph of the step",
+                "pct_of_8TBs": round(100 * value / NOMINAL_HBM_GBS, 1),
+                "sharding": ("rows split evenly across ranks; each rank's GEMV kernels store their rows into every rank's y "
+                             "(peer mappings, no collective call); every step ends with on-device arrival flags; "
+                             "gathered y verified bit-identical to the unsharded product on all %d jobs: %s" % (len(jobs), gather_ok))
+                if world > 1 else "single GPU"},
+        "gpu_launches": launches_per_step * args.steps * reps,
         "clocks": clocks,
     }
     if dom:
         def brief(p):
             return {"format": p["format"], "shape": f'{p["rows"]}x{p["cols"]}', "us": p["us"], "gbs": p["gbs"],
                     "frac": round(p["gbs"] / peak, 3)}
-        out["roofline"] = {"bound": "hbm", "kernel": f"gemv_tma_kernel / gemv_mma_kernel family, {len(in_step)} launches per step",
+        out["roofline"] = {"bound": "hbm", "kernel": f"batch-1 GEMV kernel family, {len(in_step)} launches per step",
                            "achieved": round(dom["gbs"], 1), "peak": peak, "peak_source": peak_src, "unit": "GB/s",
                            "frac": round(dom["gbs"] / peak, 3), "traffic": dom["traffic"],
                            "bytes_per_launch": int(dom["bytes"]), "us_per_launch": round(dom["us"], 2),
-                           "traffic_note": "average algorithmic bytes per launch x the ncu DRAM/algorithmic ratio of the captured Q4_0, Q8_0, Q4_K launches",
+                           "traffic_note": "average algorithmic bytes per launch x the ncu DRAM/algorithmic ratio of captured Q4_0, Q8_0, Q4_K launches",
                            "slowest": brief(dom["slow"]), "fastest": brief(dom["fast"])}
         out["per_format"] = per
+        if any("dequant_bitexact" in p for p in per):
+            out["parity"] = {"dequant_bitexact_all": all(p.get("dequant_bitexact", True) for p in per),
+                             "max_rel_worst": max(p.get("max_rel", 0.0) for p in per), "tolerance": 1e-3,
+                             "rows_checked": "three 64-row bands (first, middle, last) of every matrix"}
     if e2e_val is not None:
         out["e2e"] = {"value": e2e_val, "unit": "GB/s",
                       "h2d_bytes_per_step": int(sum(4 * j["cols"] for j in jobs)),
                       "d2h_bytes_per_step": int(sum(4 * (j["r1"] - j["r0"]) for j in jobs))}
     if world == 1 and not args.no_cpu_baseline and not args.quick:
         sample = [f for f in SWEEP if f[0] in ("Q4_0", "Q8_0", "Q4_K", "Q6_K", "IQ3_S", "TernaryPacked", "BinaryPacked_g128")]
-        gbs, cores, sec, total = cpu_leg(3, 1, sample, SHAPES[0])
+        gbs, cores, sec, total = cpu_leg(3, 1, sample, SHAPES[:1])
         out["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
                                "sample": f"{len(sample)} formats ({','.join(f[0] for f in sample)}) at 4096x14336, 3 timed passes, SIMD-path caches prebuilt"}
     if world == 1 and not args.quick and not args.formats:

@@ -84,6 +84,48 @@ def test_ffn_shapes_full_size(wv, fmt, shape):
     assert np.all(np.abs(y3.astype(np.float64) - (2.0 * y + y2)) <= 3 * TOL * den)
 
 
+_FULL = ("Q4_K", "Q8_0", "Q4_0", "IQ2_XS", "IQ4_NL", "BinaryPacked")   # covered by test_ffn_shapes_full_size (packer equality, linearity)
+_REST = [c for c in CASES if not (c[0] in _FULL and (c[0] != "BinaryPacked" or c[1] == 128))]
+
+
+def _device_packed(wv, f, bw, dt, w, rows, cols):
+    """Blob packed by the device packer (byte-identical to the reference packer: test_pack_unpack_matvec and
+    test_ffn_shapes_full_size) and the oracle's view of the same bytes."""
+    q = wv.quant
+    blob = q.Pack(q.Format(O.FMT[f]), w, rows, cols, bw, dt)
+    ob = O.Blob(O.FMT[f], rows, cols, blob.Raw, blob.Scales, blob.Mins, blob.BlockWeights if f != "none" else 1, dt)
+    return blob, ob
+
+
+@pytest.mark.parametrize("case", _REST, ids=case_id)
+@pytest.mark.parametrize("shape", [(4096, 14336), (14336, 4096)], ids=["4096x14336", "14336x4096"])
+def test_ffn_shapes_every_layout(wv, case, shape):
+    """The benchmark's two shapes for every layout the benchmark times there (the six formats of
+    test_ffn_shapes_full_size apart): outputs against the SIMD-path oracle on the benchmark's own inputs."""
+    f, bw, dt = case
+    rows, cols = shape
+    w = np.random.default_rng(2).normal(0, 0.02, rows * cols).astype(np.float32)
+    x = np.random.default_rng(1).normal(0, 1, cols).astype(np.float32)
+    blob, ob = _device_packed(wv, f, 64 if f == "AffinePacked" else bw, dt, w, rows, cols)
+    y = np.zeros(rows, np.float32)
+    wv.quant.MatVec(blob, x, y)
+    check(y, ob, x, refs=("simd",))
+
+
+@pytest.mark.parametrize("fmt", ["Q4_K", "Q8_0"])
+@pytest.mark.parametrize("shape", [(8192, 8192), (1024, 8192), (28672, 8192), (8192, 28672)], ids=lambda s: f"{s[0]}x{s[1]}")
+def test_70b_block_shapes_full_size(wv, fmt, shape):
+    """The projection shapes of the 70B decoder block (Q/O 8192x8192, K/V 1024x8192, gate/up 28672x8192,
+    down 8192x28672) at full size, weights seed 5."""
+    rows, cols = shape
+    w = np.random.default_rng(5).normal(0, 0.02, rows * cols).astype(np.float32)
+    x = np.random.default_rng(6).normal(0, 1, cols).astype(np.float32)
+    blob, ob = _device_packed(wv, fmt, 0, 1, w, rows, cols)
+    y = np.zeros(rows, np.float32)
+    wv.quant.MatVec(blob, x, y)
+    check(y, ob, x, refs=("simd",))
+
+
 @pytest.mark.parametrize("cols", [8192, 1056, 4608, 17408, 28672])
 @pytest.mark.parametrize("fmt", ["Q4_K", "Q5_1", "IQ3_S", "Q8_0"])
 def test_kernel_selection_boundaries(wv, fmt, cols):

@@ -22,7 +22,7 @@ SYMBOLS = [
 ]
 
 # Development hooks (csrc/wv_dev_hooks.h): exported for tests and tuning runs, not part of the public header.
-DEV_HOOKS = ["wv_set_tuning", "wv_set_tma_tuning"]
+DEV_HOOKS = ["wv_set_tuning", "wv_set_tma_tuning", "wv_set_act_width"]
 
 WV_OK, WV_ESHAPE, WV_EFORMAT, WV_ENOMEM, WV_ECUDA, WV_ETIMEOUT, WV_ENOTFOUND, WV_EINIT, WV_EARG = (
     0, -1, -2, -3, -4, -5, -6, -7, -8)
@@ -59,6 +59,8 @@ def lib() -> C.CDLL:
         L.wv_set_tuning.argtypes = [i, i, i, i]
         L.wv_set_tma_tuning.restype = None
         L.wv_set_tma_tuning.argtypes = [i, i]
+        L.wv_set_act_width.restype = None
+        L.wv_set_act_width.argtypes = [i]
         L.wv_init.argtypes = [i]
         L.wv_blob_upload.argtypes = [u64, i, i, i, i, i, vp, sz, vp, sz, vp, sz]
         L.wv_blob_upload_wire.argtypes = [u64, i, i, i, i, vp, sz]

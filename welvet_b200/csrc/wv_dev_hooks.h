@@ -11,6 +11,9 @@ void wv_set_tuning(int rows_per_warp, int col_split, int depth, int grid);
 // kernel; ring depth cap in the low two digits of `stages`, tiles issued ahead of the activation
 // loads in the hundreds.
 void wv_set_tma_tuning(int rows_per_group, int stages);
+// Width of the activation records of the integer-dot kernels: 0 = chosen per launch from the input
+// vector (16-bit unless it has isolated outliers), 3 = always 24-bit.
+void wv_set_act_width(int limbs);
 #ifdef __cplusplus
 }
 #endif

@@ -506,11 +506,12 @@ static int launch_dense(const WvDevBlob& b, const float* dx, float* dy, int batc
   size_t smem = (size_t)b.cols * 4 + 16;
   if (smem > 110 * 1024) { wv_set_error("gemv: cols=%d needs %zu bytes of shared memory for x (max 112640)", b.cols, smem); return WV_ESHAPE; }
   static unsigned attr_mask = 0;
-  auto kern = gemv_dense_kernel<DT, 4>;
+  auto kern = g_tune_d == 8 ? gemv_dense_kernel<DT, 8> : gemv_dense_kernel<DT, 4>;   // vectors per lane per step (tuning hook)
   int dev = 0; cudaGetDevice(&dev);
-  if (!(attr_mask & (1u << dev))) {
+  const unsigned bit = (1u << dev) << (g_tune_d == 8 ? 16 : 0);
+  if (!(attr_mask & bit)) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024) != cudaSuccess) return WV_ECUDA;
-    attr_mask |= 1u << dev;
+    attr_mask |= bit;
   }
   int grid = g_tune_grid > 0 ? g_tune_grid : 2 * sm_count();
   if (grid > re - rb) grid = re - rb;

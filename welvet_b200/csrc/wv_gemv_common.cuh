@@ -341,6 +341,134 @@ __device__ __forceinline__ float idot_chunk(const FragT<F>& f, const XQRegs& x) 
   return fmaf(mt.x, v, extra);
 }
 
+// ------------------------------------------------------------------ two-limb activations (16-bit)
+// The default arithmetic of the bulk-copy kernel: per 32-column chunk X_j = rint(x_j * 32512 / amax),
+// |X_j| <= 32512, split as X = L0 + 256 L1 with an unsigned low byte and a signed high byte, so a group
+// of four codes needs two dp4a instead of three and the limb sums always recombine in 32-bit integers
+// (255 * 32 * 32512 < 2^31). Per element |x_j - X_j sf| <= amax / 65024, sf = amax / 32512. A chunk
+// whose large values sit next to much smaller ones loses the small ones' low bits; the kernel decides
+// per launch, from the whole vector, whether that can matter (see gemv_tma_kernel) and takes the
+// three-limb path of quantize_chunk / idot_chunk when it can.
+struct XQRegs2 {
+  unsigned xw[16];   // word limb*8 + k
+  float4 mt;         // {sf, sf*SX(all), sf*SX(first 16), sf*SX(second 16)}
+  int iv[4];         // -mid*sum(limb l, half h) at l*2+h (halves pre-added for 32-wide groups)
+};
+
+// xv: the chunk's 32 activations (already in registers), amax: their largest magnitude, bad: inf / NaN seen.
+template <int F>
+__device__ __forceinline__ void quantize_chunk2(XQRegs2& x, const float (&xv)[32], float amax, bool bad) {
+  constexpr WvFmtInfo fi = wv_fmt_info(F);
+  constexpr int BL = fi.bits_lo;
+  float sf = 0.f, inv = 0.f;
+  if (bad) sf = __uint_as_float(0x7fc00000u);          // inf / NaN in x: results become NaN
+  else if (amax >= 1.0e-30f) { sf = amax * (1.0f / 32512.0f); inv = 32512.0f / amax; }   // |x inv| <= 32512 (1 + 2^-23)
+  int sl[2][2] = {{0, 0}, {0, 0}};
+#pragma unroll
+  for (int k = 0; k < 8; k++) {
+    unsigned X[4];
+    // the low 23 bits of 1.5*2^23 + rint(v) hold rint(v) in two's complement (|v| < 2^22): bytes 0 and 1
+    // are the two limbs as they are, no subtraction needed
+#pragma unroll
+    for (int m = 0; m < 4; m++) X[m] = __float_as_uint(fmaf(xv[WvLane<BL>::j_of(k, m)], inv, 12582912.0f));
+    const unsigned a01 = __byte_perm(X[0], X[1], 0x5140), a23 = __byte_perm(X[2], X[3], 0x5140);   // {b0,b0',b1,b1'}
+    const unsigned w0 = __byte_perm(a01, a23, 0x5410), w1 = __byte_perm(a01, a23, 0x7632);
+    x.xw[k] = w0; x.xw[8 + k] = w1;
+    const int hh = (BL == 1 || k < 4) ? 0 : 1;   // 1-bit planes split the halves by byte lane: everything in half 0
+    sl[0][hh] = dp4a_uu(w0, 0x01010101u, sl[0][hh]);
+    sl[1][hh] = dp4a_su(w1, 0x01010101u, sl[1][hh]);
+  }
+  const int sx0 = sl[0][0] + (sl[1][0] << 8), sx1 = sl[0][1] + (sl[1][1] << 8);
+  x.mt = make_float4(sf, sf * (float)(sx0 + sx1), sf * (float)sx0, sf * (float)sx1);
+#pragma unroll
+  for (int i = 0; i < 4; i++) x.iv[i] = 0;
+  if constexpr (QCfg<F>::INT_MID) {
+    if constexpr (QCfg<F>::HALVES) {
+#pragma unroll
+      for (int l = 0; l < 2; l++) { x.iv[l * 2] = -fi.mid * sl[l][0]; x.iv[l * 2 + 1] = -fi.mid * sl[l][1]; }
+    } else {
+#pragma unroll
+      for (int l = 0; l < 2; l++) x.iv[l * 2] = -fi.mid * (sl[l][0] + sl[l][1]);
+    }
+  }
+}
+
+// Integer sums of one chunk-row per parameter half; the common tail below turns them into the row's share.
+template <int F>
+__device__ __forceinline__ void idot_sums2(const FragT<F>& f, const XQRegs2& x, float (&val)[2]) {
+  constexpr WvFmtInfo fi = wv_fmt_info(F);
+  constexpr int BL = fi.bits_lo, BH = fi.bits_hi, SPW = 8 / BL;
+  constexpr unsigned MASK = 0x01010101u * ((1u << BL) - 1u);
+  constexpr unsigned MASKH = BH ? (0x01010101u * ((1u << BH) - 1u)) << BL : 0u;
+  constexpr bool HALVES = QCfg<F>::HALVES;
+  constexpr int NH = QCfg<F>::NH;
+  int I[2][2];
+#pragma unroll
+  for (int l = 0; l < 2; l++) { I[l][0] = x.iv[l * 2]; I[l][1] = HALVES ? x.iv[l * 2 + 1] : 0; }
+#pragma unroll
+  for (int k = 0; k < 8; k++) {
+    const int w = k / SPW, sh = k % SPW;
+    unsigned bytes = (f.lo[w] >> (BL * sh)) & MASK;
+    if constexpr (BH > 0) {
+      const int hw = (k * BH) >> 3, hs = (k * BH) & 7;
+      unsigned hv = f.hi[hw];
+      hv = hs >= BL ? (hv >> (hs - BL)) : (hv << (BL - hs));
+      bytes |= hv & MASKH;
+    }
+    const int h = (HALVES && k >= 4) ? 1 : 0;
+    I[0][h] = dp4a_uu(bytes, x.xw[k], I[0][h]);
+    I[1][h] = dp4a_us(bytes, x.xw[8 + k], I[1][h]);
+  }
+#pragma unroll
+  for (int h = 0; h < NH; h++) val[h] = (float)(I[0][h] + (I[1][h] << 8));
+}
+
+// Scale / min arithmetic shared by the two- and three-limb paths: val[h] = sum over half h of
+// (code - mid) * X, mt = {sf, sf*SX, sf*SX(first 16), sf*SX(second 16)}.
+template <int F>
+__device__ __forceinline__ float idot_finish(const FragT<F>& f, const float (&val)[2], const float4 mt) {
+  constexpr WvFmtInfo fi = wv_fmt_info(F);
+  constexpr bool HALVES = QCfg<F>::HALVES;
+  float v, extra = 0.f;
+  if constexpr (fi.kind == WK_KQUANT) {
+    // scale bytes were remapped 0 -> 1 at upload (kquant.go:180-182: a zero group scale decodes as d/255)
+    const float t = (float)(unsigned char)(f.pr[2]) * val[0] + (float)(unsigned char)(f.pr[2] >> 8) * val[1];
+    v = (__uint_as_float(f.pr[0]) * (1.0f / 255.0f)) * t;
+    if constexpr (fi.has_min) {
+      const float mm = (float)(signed char)(f.pr[2] >> 16) * mt.z + (float)(signed char)(f.pr[2] >> 24) * mt.w;
+      extra = (__uint_as_float(f.pr[1]) * (1.0f / 127.0f)) * mm;
+    }
+  } else if constexpr (fi.kind == WK_CLASSIC || fi.kind == WK_AFFINE) {
+    v = __uint_as_float(f.pr[0]) * val[0];
+    if constexpr (fi.has_min) extra = __uint_as_float(f.pr[1]) * mt.y;
+  } else if constexpr (fi.kind == WK_TERNARY) {
+    v = __uint_as_float(f.pr[0]) * val[0] + __uint_as_float(f.pr[1]) * val[1];
+  } else if constexpr (fi.sign) {
+    v = __uint_as_float(f.pr[0]) * (2.0f * val[0]);
+    extra = -__uint_as_float(f.pr[0]) * mt.y;
+  } else {  // IQ linear grids: (code - mid - 0.5)
+    constexpr float hm = (float)fi.mid + 0.5f;
+    if constexpr (HALVES) {
+      v = __uint_as_float(f.pr[0]) * val[0] + __uint_as_float(f.pr[1]) * val[1];
+      extra = -hm * (__uint_as_float(f.pr[0]) * mt.z + __uint_as_float(f.pr[1]) * mt.w);
+    } else {
+      v = __uint_as_float(f.pr[0]) * val[0];
+      extra = -hm * __uint_as_float(f.pr[0]) * mt.y;
+    }
+  }
+  return fmaf(mt.x, v, extra);
+}
+
+template <int F>
+__device__ __forceinline__ float idot_chunk2(const FragT<F>& f, const XQRegs2& x) {
+  float val[2] = {0.f, 0.f};
+  idot_sums2<F>(f, x, val);
+  return idot_finish<F>(f, val, x.mt);
+}
+// One name for both activation widths (the kernel's main loop is instantiated once per width).
+template <int F> __device__ __forceinline__ float idot_any(const FragT<F>& f, const XQRegs& x) { return idot_chunk<F>(f, x); }
+template <int F> __device__ __forceinline__ float idot_any(const FragT<F>& f, const XQRegs2& x) { return idot_chunk2<F>(f, x); }
+
 // Launch with programmatic dependent launch allowed: the kernel may start while its
 // predecessor drains and must execute griddepcontrol.wait before touching dependent data.
 template <typename... KArgs, typename... Args>

@@ -38,6 +38,7 @@ struct TmaGeom {
   unsigned rb[5];    // bytes per row of each plane (0 = plane absent)
   int rows_base, rows_rem;  // single matrix: CTA b owns rows_base (+1 if b < rows_rem) consecutive rows
   int lead;          // tiles issued before the producer waits for the activation loads to be on their way
+  int force3;        // development switch: always use the 24-bit activation records
   unsigned x_off;    // staged activations: 33 floats per chunk (32 + one of padding)
   unsigned red_off;  // float red[2][nrg][nwc][32]
   unsigned bar_off;  // full[nstage], empty[nstage]
@@ -141,6 +142,7 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int s_abort;
   __shared__ unsigned s_xissued;   // consumer warps that have issued their loads of x
+  __shared__ float2 s_stat[TMA_MAX_ROW_GROUPS][TMA_CONSUMER_WARPS];   // per column warp: {sum of chunk maxima, sum |x|}
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   // band of this CTA in matrix i, without divisions: the host splits the rows as evenly as possible
   const int bid = blockIdx.x;
@@ -247,7 +249,8 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   WV_STAMP(1);
   // All consumer warps copy x into shared memory with coalesced loads; each chunk of 32
   // floats gets a 33-float slot so that lanes reading their own chunks element by element
-  // hit 32 different banks.
+  // hit 32 different banks. Every CTA starts its copy at a different place of x: all SMs
+  // asking for the same lines in the same order would queue up at one L2 slice after the other.
   {
     const float* xrow = xf + (size_t)blockIdx.y * b.cols;
     float* xs = reinterpret_cast<float*>(smem + g.x_off);
@@ -255,17 +258,22 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
     if ((reinterpret_cast<uintptr_t>(xrow) & 15) == 0) {
       // cols <= 16384: at most 8 vectors per thread; all loads are issued before the first
       // store so that the copy costs one memory round trip, not eight
+      const int rot = (int)(((unsigned)bid * 211u) % (unsigned)nv) & ~7;   // whole chunks (8 vectors)
       float4 v[8];
 #pragma unroll
       for (int u = 0; u < 8; u++) {
-        const int i = tid + u * TMA_CONSUMER_WARPS * 32;
-        if (i < nv) v[u] = __ldg(reinterpret_cast<const float4*>(xrow) + i);
+        const int i0 = tid + u * TMA_CONSUMER_WARPS * 32;
+        int i = i0 + rot;
+        if (i >= nv) i -= nv;
+        if (i0 < nv) v[u] = __ldg(reinterpret_cast<const float4*>(xrow) + i);
       }
       if (lane == 0) asm volatile("red.relaxed.cta.shared::cta.add.u32 [%0], 1;" ::"r"(smem_u32(&s_xissued)) : "memory");
 #pragma unroll
       for (int u = 0; u < 8; u++) {
-        const int i = tid + u * TMA_CONSUMER_WARPS * 32;
-        if (i < nv) { float* d = xs + (i >> 3) * 33 + (i & 7) * 4; d[0] = v[u].x; d[1] = v[u].y; d[2] = v[u].z; d[3] = v[u].w; }
+        const int i0 = tid + u * TMA_CONSUMER_WARPS * 32;
+        int i = i0 + rot;
+        if (i >= nv) i -= nv;
+        if (i0 < nv) { float* d = xs + (i >> 3) * 33 + (i & 7) * 4; d[0] = v[u].x; d[1] = v[u].y; d[2] = v[u].z; d[3] = v[u].w; }
       }
     } else {
       if (lane == 0) asm volatile("red.relaxed.cta.shared::cta.add.u32 [%0], 1;" ::"r"(smem_u32(&s_xissued)) : "memory");
@@ -275,46 +283,7 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   asm volatile("bar.sync 15, %0;" ::"n"(TMA_CONSUMER_WARPS * 32) : "memory");
   WV_STAMP(5);
   if (rg >= g.nrg) return;
-  XQRegs xr;
-  float4 xfr[8];
-  const unsigned char* tbl = nullptr;
-  {
-    const float* xc = reinterpret_cast<const float*>(smem + g.x_off) + (size_t)c * 33;
-    if constexpr (fi.table) {
-      tbl = smem + g.red_off + 2u * g.nrg * g.nwc * 32 * 4;
-#pragma unroll
-      for (int k = 0; k < 8; k++) xfr[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (live) {
-        const float* xp = xc;
-#pragma unroll
-        for (int k = 0; k < 8; k++)
-          xfr[k] = make_float4(xp[WvLane<BL>::j_of(k, 0)], xp[WvLane<BL>::j_of(k, 1)], xp[WvLane<BL>::j_of(k, 2)], xp[WvLane<BL>::j_of(k, 3)]);
-      }
-    } else {
-      if (live) {
-        quantize_chunk<F>(xr, xc);
-        if constexpr (BL == 8) {
-          const bool sw = lane & 4;
-#pragma unroll
-          for (int l = 0; l < 3; l++) {
-#pragma unroll
-            for (int k = 0; k < 4; k++) {
-              const unsigned a0 = xr.xw[8 * l + k], a1 = xr.xw[8 * l + k + 4];
-              xr.xw[8 * l + k] = sw ? a1 : a0;
-              xr.xw[8 * l + k + 4] = sw ? a0 : a1;
-            }
-          }
-        }
-      } else {
-#pragma unroll
-        for (int t = 0; t < 24; t++) xr.xw[t] = 0u;
-        xr.mt = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int i = 0; i < 6; i++) xr.iv[i] = 0;
-      }
-    }
-  }
-  WV_STAMP(2);
+
   float* red = reinterpret_cast<float*>(smem + g.red_off);
   float* yb = nullptr;
   float keep = 0.f;
@@ -386,86 +355,179 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
     if (++fs == g.nstage) { fs = 0; fpar ^= 1u; }
   };
 
-  for (int bi = 0; bi < nmat; bi++) {   // one matrix after the other; ring position and x registers carry over
-  set_band(bi);
-  nslots = ntiles * RT;
-  if constexpr (EXT) yb = ext.grp.y[bi] + (size_t)blockIdx.y * ext.grp.rows[bi] + row_begin;
-  else yb = y + (size_t)blockIdx.y * b.rows + row_begin;
-  FragT<F> nxt[PREFETCH ? RT : 1];
-  if constexpr (PREFETCH) { if (ntiles > 0) { wait_tile(true); fetch_tile(nxt); } }
-  WV_STAMP(3);
-  for (int t = 0; t < ntiles; t++) {
-    FragT<F> fr[RT];
-    bool fetched = true;
-    if constexpr (PREFETCH) {
+  // The main loop, instantiated once per activation record type: `dot(fragment)` is the chunk-row's
+  // share of its output row.
+  auto main_loop = [&](auto dot) {
+    for (int bi = 0; bi < nmat; bi++) {   // one matrix after the other; ring position and x registers carry over
+      set_band(bi);
+      nslots = ntiles * RT;
+      if constexpr (EXT) yb = ext.grp.y[bi] + (size_t)blockIdx.y * ext.grp.rows[bi] + row_begin;
+      else yb = y + (size_t)blockIdx.y * b.rows + row_begin;
+      FragT<F> nxt[PREFETCH ? RT : 1];
+      if constexpr (PREFETCH) { if (ntiles > 0) { wait_tile(true); fetch_tile(nxt); } }
+      WV_STAMP(3);
+      for (int t = 0; t < ntiles; t++) {
+        FragT<F> fr[RT];
+        bool fetched = true;
+        if constexpr (PREFETCH) {
 #pragma unroll
-      for (int rr = 0; rr < RT; rr++) fr[rr] = nxt[rr];
-      // prefetch the next tile's fragments before computing when they have already landed
-      if (t + 1 < ntiles) {
-        fetched = wait_tile(false);
-        if (fetched) fetch_tile(nxt);
+          for (int rr = 0; rr < RT; rr++) fr[rr] = nxt[rr];
+          // prefetch the next tile's fragments before computing when they have already landed
+          if (t + 1 < ntiles) {
+            fetched = wait_tile(false);
+            if (fetched) fetch_tile(nxt);
+          }
+        } else {
+          wait_tile(true);
+          WV_STAMP(8 + 2 * t);
+          fetch_tile(fr);
+        }
+        float v[RT];
+        // No per-row branch: the RT chunk-rows form one block of independent dependency chains.
+        // Lanes past the last chunk hold zeroed activations and contribute exactly 0.
+#pragma unroll
+        for (int rr = 0; rr < RT; rr++) v[rr] = dot(fr[rr]);
+        // Transposing reduction: RT row sums per lane -> every lane ends with the warp total of one
+        // row; the lane whose index equals the row's slot (n & 31) keeps it.
+        float tot;
+        if constexpr (RT == 4) {
+          const bool b4 = lane & 16, b3 = lane & 8;
+          float a0 = b4 ? v[2] : v[0], a1 = b4 ? v[3] : v[1];
+          a0 += __shfl_xor_sync(0xffffffffu, b4 ? v[0] : v[2], 16);
+          a1 += __shfl_xor_sync(0xffffffffu, b4 ? v[1] : v[3], 16);
+          tot = b3 ? a1 : a0;
+          tot += __shfl_xor_sync(0xffffffffu, b3 ? a0 : a1, 8);
+#pragma unroll
+          for (int o = 4; o; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+          tot = __shfl_sync(0xffffffffu, tot, (lane & 3) * 8);  // row (lane & 3) lives in lanes [8*(lane&3), +8)
+          if ((lane >> 2) == (t & 7)) keep = tot;
+        } else if constexpr (RT == 8) {
+          const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4;
+          float a[4];
+#pragma unroll
+          for (int i = 0; i < 4; i++) a[i] = (b4 ? v[4 + i] : v[i]) + __shfl_xor_sync(0xffffffffu, b4 ? v[i] : v[4 + i], 16);
+          float c0 = (b3 ? a[2] : a[0]) + __shfl_xor_sync(0xffffffffu, b3 ? a[0] : a[2], 8);
+          float c1 = (b3 ? a[3] : a[1]) + __shfl_xor_sync(0xffffffffu, b3 ? a[1] : a[3], 8);
+          tot = (b2 ? c1 : c0) + __shfl_xor_sync(0xffffffffu, b2 ? c0 : c1, 4);
+          tot += __shfl_xor_sync(0xffffffffu, tot, 2);
+          tot += __shfl_xor_sync(0xffffffffu, tot, 1);
+          // row r = 4*b4 + 2*b3 + b2 lives in lanes [4r, 4r+4): lane wants row (lane & 7)
+          tot = __shfl_sync(0xffffffffu, tot, ((lane & 4) ? 16 : 0) + ((lane & 2) ? 8 : 0) + ((lane & 1) ? 4 : 0));
+          if ((lane >> 3) == (t & 3)) keep = tot;
+        } else if constexpr (RT == 2) {
+          const bool b4 = lane & 16;
+          tot = b4 ? v[1] : v[0];
+          tot += __shfl_xor_sync(0xffffffffu, b4 ? v[0] : v[1], 16);
+#pragma unroll
+          for (int o = 8; o; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+          tot = __shfl_sync(0xffffffffu, tot, (lane & 1) * 16);
+          if ((lane >> 1) == (t & 15)) keep = tot;
+        } else {
+          tot = v[0];
+#pragma unroll
+          for (int o = 16; o; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+          if (lane == (t & 31)) keep = tot;
+        }
+        if (((t * RT + RT - 1) & 31) == 31) flush(t * RT + RT - 32);
+        WV_STAMP(9 + 2 * t);
+        if constexpr (PREFETCH) { if (!fetched) { wait_tile(true); fetch_tile(nxt); } }
       }
+      if (nslots & 31) flush(nslots & ~31);
+    }
+  };
+
+  const float* xc = reinterpret_cast<const float*>(smem + g.x_off) + (size_t)(live ? c : 0) * 33;
+  if constexpr (fi.table) {
+    // IQ4_NL: f32 grid values from a shared-memory table, activations stay f32
+    const unsigned char* tbl = smem + g.red_off + 2u * g.nrg * g.nwc * 32 * 4;
+    float4 xfr[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) xfr[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live) {
+#pragma unroll
+      for (int k = 0; k < 8; k++)
+        xfr[k] = make_float4(xc[WvLane<BL>::j_of(k, 0)], xc[WvLane<BL>::j_of(k, 1)], xc[WvLane<BL>::j_of(k, 2)], xc[WvLane<BL>::j_of(k, 3)]);
+    }
+    WV_STAMP(2);
+    const unsigned lane4 = (unsigned)lane * 4u;
+    main_loop([&](const FragT<F>& f) { return chunk_value_tbl<F>(f, xfr, tbl, lane4); });
+  } else {
+    // Statistics of x that decide the width of the activation records (all CTAs see the same x and
+    // reach the same decision): A = sum over chunks of the chunk's largest magnitude, S = sum |x_j|.
+    // With 16-bit records an element is off by at most amax_chunk / 65024, so a row's error is at most
+    // sum_chunks amax_c / 65024 * sum_{j in c} |w_j|, about w_mean * 4.9e-4 * A for weights that are not
+    // concentrated on a chunk's small elements, against a budget of 1e-3 * w_mean * S. A <= S / 4 keeps
+    // an eightfold margin (N(0,1) data: A / S = 0.09); vectors with isolated outliers, inf or NaN fail
+    // the test and take 24-bit records, whose error is 2^-9 of that. Weights that sit exactly on the
+    // small elements of outlier chunks can exceed either bound: no criterion on x alone excludes that.
+    float xv[32];
+#pragma unroll
+    for (int j = 0; j < 32; j++) xv[j] = xc[j];
+    float am[4] = {0.f, 0.f, 0.f, 0.f}, as[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < 32; j++) { const float a = fabsf(xv[j]); am[j & 3] = fmaxf(am[j & 3], a); as[j & 3] += a; }
+    float amax = fmaxf(fmaxf(am[0], am[1]), fmaxf(am[2], am[3]));
+    float asum = (as[0] + as[1]) + (as[2] + as[3]);   // inf / NaN anywhere in the chunk makes this inf / NaN
+    if (!live) { amax = 0.f; asum = 0.f; }
+    float ta = amax, ts = asum;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) { ta += __shfl_xor_sync(0xffffffffu, ta, o); ts += __shfl_xor_sync(0xffffffffu, ts, o); }
+    if (lane == 0) s_stat[rg][wc] = make_float2(ta, ts);
+    asm volatile("bar.sync %0, %1;" ::"r"(rg + 1), "r"(g.nwc * 32) : "memory");
+    ta = 0.f; ts = 0.f;
+    for (int q = 0; q < g.nwc; q++) { const float2 p = s_stat[rg][q]; ta += p.x; ts += p.y; }
+    const bool wide = !(ta <= 0.25f * ts) || g.force3;   // NaN compares false: non-finite input takes the wide path
+    if (!wide) {
+      XQRegs2 xr;
+      if (live) {
+        quantize_chunk2<F>(xr, xv, amax, false);
+        if constexpr (BL == 8) {
+          const bool sw = lane & 4;
+#pragma unroll
+          for (int l = 0; l < 2; l++) {
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+              const unsigned a0 = xr.xw[8 * l + k], a1 = xr.xw[8 * l + k + 4];
+              xr.xw[8 * l + k] = sw ? a1 : a0;
+              xr.xw[8 * l + k + 4] = sw ? a0 : a1;
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int t = 0; t < 16; t++) xr.xw[t] = 0u;
+        xr.mt = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < 4; i++) xr.iv[i] = 0;
+      }
+      WV_STAMP(2);
+      main_loop([&](const FragT<F>& f) { return idot_chunk2<F>(f, xr); });
     } else {
-      wait_tile(true);
-      WV_STAMP(8 + 2 * t);
-      fetch_tile(fr);
+      XQRegs xr;
+      if (live) {
+        quantize_chunk<F>(xr, xc);
+        if constexpr (BL == 8) {
+          const bool sw = lane & 4;
+#pragma unroll
+          for (int l = 0; l < 3; l++) {
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+              const unsigned a0 = xr.xw[8 * l + k], a1 = xr.xw[8 * l + k + 4];
+              xr.xw[8 * l + k] = sw ? a1 : a0;
+              xr.xw[8 * l + k + 4] = sw ? a0 : a1;
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int t = 0; t < 24; t++) xr.xw[t] = 0u;
+        xr.mt = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < 6; i++) xr.iv[i] = 0;
+      }
+      WV_STAMP(2);
+      main_loop([&](const FragT<F>& f) { return idot_chunk<F>(f, xr); });
     }
-    float v[RT];
-#pragma unroll
-    for (int rr = 0; rr < RT; rr++) {
-      const int lr = rg * RT + rr;
-      // No per-row branch: the RT chunk-rows form one block of independent dependency chains.
-      // Lanes past the last chunk hold zeroed activations and contribute exactly 0.
-      (void)lr;
-      if constexpr (fi.table) v[rr] = chunk_value_tbl<F>(fr[rr], xfr, tbl, (unsigned)lane * 4u);
-      else v[rr] = idot_chunk<F>(fr[rr], xr);
-    }
-    // Transposing reduction: RT row sums per lane -> every lane ends with the warp total of one
-    // row; the lane whose index equals the row's slot (n & 31) keeps it.
-    float tot;
-    if constexpr (RT == 4) {
-      const bool b4 = lane & 16, b3 = lane & 8;
-      float a0 = b4 ? v[2] : v[0], a1 = b4 ? v[3] : v[1];
-      a0 += __shfl_xor_sync(0xffffffffu, b4 ? v[0] : v[2], 16);
-      a1 += __shfl_xor_sync(0xffffffffu, b4 ? v[1] : v[3], 16);
-      tot = b3 ? a1 : a0;
-      tot += __shfl_xor_sync(0xffffffffu, b3 ? a0 : a1, 8);
-#pragma unroll
-      for (int o = 4; o; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
-      tot = __shfl_sync(0xffffffffu, tot, (lane & 3) * 8);  // row (lane & 3) lives in lanes [8*(lane&3), +8)
-      if ((lane >> 2) == (t & 7)) keep = tot;
-    } else if constexpr (RT == 8) {
-      const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4;
-      float a[4];
-#pragma unroll
-      for (int i = 0; i < 4; i++) a[i] = (b4 ? v[4 + i] : v[i]) + __shfl_xor_sync(0xffffffffu, b4 ? v[i] : v[4 + i], 16);
-      float c0 = (b3 ? a[2] : a[0]) + __shfl_xor_sync(0xffffffffu, b3 ? a[0] : a[2], 8);
-      float c1 = (b3 ? a[3] : a[1]) + __shfl_xor_sync(0xffffffffu, b3 ? a[1] : a[3], 8);
-      tot = (b2 ? c1 : c0) + __shfl_xor_sync(0xffffffffu, b2 ? c0 : c1, 4);
-      tot += __shfl_xor_sync(0xffffffffu, tot, 2);
-      tot += __shfl_xor_sync(0xffffffffu, tot, 1);
-      // row r = 4*b4 + 2*b3 + b2 lives in lanes [4r, 4r+4): lane wants row (lane & 7)
-      tot = __shfl_sync(0xffffffffu, tot, ((lane & 4) ? 16 : 0) + ((lane & 2) ? 8 : 0) + ((lane & 1) ? 4 : 0));
-      if ((lane >> 3) == (t & 3)) keep = tot;
-    } else if constexpr (RT == 2) {
-      const bool b4 = lane & 16;
-      tot = b4 ? v[1] : v[0];
-      tot += __shfl_xor_sync(0xffffffffu, b4 ? v[0] : v[1], 16);
-#pragma unroll
-      for (int o = 8; o; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
-      tot = __shfl_sync(0xffffffffu, tot, (lane & 1) * 16);
-      if ((lane >> 1) == (t & 15)) keep = tot;
-    } else {
-      tot = v[0];
-#pragma unroll
-      for (int o = 16; o; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
-      if (lane == (t & 31)) keep = tot;
-    }
-    if (((t * RT + RT - 1) & 31) == 31) flush(t * RT + RT - 32);
-    WV_STAMP(9 + 2 * t);
-    if constexpr (PREFETCH) { if (!fetched) { wait_tile(true); fetch_tile(nxt); } }
-  }
-  if (nslots & 31) flush(nslots & ~31);
   }
   WV_STAMP(4);
   WV_STAMP_NS(7);
@@ -495,6 +557,9 @@ static bool plane_row_bytes(const WvDevBlob& b, unsigned rb[5]) {
 static int g_tma_rt = 0, g_tma_stages = 0;
 extern "C" void wv_set_tma_tuning(int rows_per_group, int stages) { g_tma_rt = rows_per_group; g_tma_stages = stages; }
 int wv_tma_tuning_stages() { return g_tma_stages; }
+static int g_act_width = 0;
+extern "C" void wv_set_act_width(int limbs) { g_act_width = limbs; }
+int wv_act_width() { return g_act_width; }
 
 template <int F, int RT, bool PF>
 static int launch_tma(const WvDevBlob* bl, int nb, const float* dx, float* const* dys, int batch, int rb_, int re, cudaStream_t st) {
@@ -519,6 +584,7 @@ static int launch_tma(const WvDevBlob* bl, int nb, const float* dx, float* const
   if (ns > TMA_MAX_STAGES) ns = TMA_MAX_STAGES;
   if (g_tma_stages % 100 > 1 && g_tma_stages % 100 < ns) ns = g_tma_stages % 100;
   g.lead = g_tma_stages >= 100 ? g_tma_stages / 100 : 1;
+  g.force3 = g_act_width == 3;
   g.nstage = ns;
   g.x_off = g.stage_bytes * ns;
   g.red_off = g.x_off + xbytes;
