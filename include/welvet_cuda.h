@@ -91,6 +91,42 @@ int wv_matvec_dev(uint64_t key, const float* dx, float* dy, int batch, int in, i
 int wv_matvec_dev_multi(const uint64_t* keys, int n, const float* dx, float* const* dy, int batch, int in, const int* out,
                         void* stream);
 
+/* Fused epilogues of the grouped launch (batch 1, device pointers, asynchronous).
+ * wv_matvec_dev_swiglu: h[out] = silu(W_gate x) * (W_up x), the SwiGLU gate product of swiglu.forwardHost
+ * (layers/swiglu/cpu.go:29-52; arithmetic of simd.SiluMulF32, simd/silu.go:14-27: g / (1 + exp(-g)) * u in
+ * float64, rounded to f32) inside the gate|up launch, as the reference's fused shader does
+ * (fusedgpu/shaders.go:159-222): gate and up are never written out. Both matrices must have `out` rows.
+ * wv_matvec_dev_add: y = W x + residual — the projection followed by residualAddInPlace
+ * (model/transformer/forward.go:65,75, scratch.go:33-41; fused precedent fusedgpu/hybrid_shaders.go:82);
+ * dy may alias dresidual (h += W x).
+ * Shapes the grouped kernel does not take run as separate launches with the same results. */
+int wv_matvec_dev_swiglu(uint64_t key_gate, uint64_t key_up, const float* dx, float* dh, int in, int out, void* stream);
+int wv_matvec_dev_add(uint64_t key, const float* dx, const float* dresidual, float* dy, int in, int out, void* stream);
+
+/* The steps between the projections of a decoder block in single-token decode, on the device, so that
+ * activations stay in HBM from one GEMV to the next (the reference runs them on the host in float64).
+ * wv_rmsnorm_dev: y[r, i] = x[r, i] * inv_r * gamma[i], inv_r = 1 / sqrt(mean(x_r^2) + eps)
+ *   (rmsnorm.forwardHost, layers/rmsnorm/cpu.go:32-90; sum and scale in float64).
+ * wv_rope_cache_dev: applyRoPE (layers/mha/rope.go:6-21; pairs (d, d + head_dim/2), angle pos / theta^(2d/head_dim),
+ *   float64 trigonometry) on the token's Q [num_heads * head_dim] in place and on its K [num_kv_heads * head_dim],
+ *   then K and V go into row pos % max_seq_len of the caches [max_seq_len, num_kv_heads * head_dim]
+ *   (forwardHost, layers/mha/cpu.go:184-207). theta <= 0 leaves Q and K unrotated.
+ * wv_attn_decode_dev: attnForward (layers/mha/attn.go:15-120) for one query token under the causal mask: softmax
+ *   of q.k * scale over cache positions 0 .. kv_len-1 (position p in row p % max_seq_len), grouped-query heads
+ *   (head h reads kv head h / (num_heads / num_kv_heads)), out[num_heads * head_dim] = sum w v. head_dim <= 256
+ *   and a multiple of 4; no ALiBi, dropout or sigmoid scores. Uses library-owned scratch for split results:
+ *   the first call for a larger shape allocates it (make that call before a stream capture) and calls on
+ *   different streams must not overlap.
+ * wv_silu_mul_dev: out[i] = silu(gate[i]) * up[i] (simd.SiluMulF32, simd/silu.go:7-27).
+ * wv_residual_add_dev: dst[i] += add[i] (residualAddInPlace, model/transformer/scratch.go:33-41). */
+int wv_rmsnorm_dev(const float* dx, const float* dgamma, float* dy, int rows, int dim, double eps, void* stream);
+int wv_rope_cache_dev(float* dq, const float* dk, const float* dv, float* dcache_k, float* dcache_v, int pos, int max_seq_len,
+                      int num_heads, int num_kv_heads, int head_dim, double theta, void* stream);
+int wv_attn_decode_dev(const float* dq, const float* dcache_k, const float* dcache_v, float* dout, int num_heads, int num_kv_heads,
+                       int head_dim, int kv_len, int max_seq_len, float scale, void* stream);
+int wv_silu_mul_dev(const float* dgate, const float* dup, float* dout, int n, void* stream);
+int wv_residual_add_dev(float* ddst, const float* dadd, int n, void* stream);
+
 /* Greedy pick on the device — sampling.ArgMax (model/sampling/argmax.go:4-18; the reference's fused path does the same
  * in a shader, fusedgpu/shaders.go:471-510): index of the first strict maximum of n device floats, so that the
  * 128256 logits of an LM head need not be read back. wv_argmax_dev writes the index to device memory on `stream`;
@@ -135,6 +171,15 @@ int wv_matvec_dev_static(uint64_t key, const float* dx, float* dy, int in, int o
  * barrier between steps, or stream-ordered events), as it would around any collective. */
 int wv_matvec_dev_gather(uint64_t key, const float* dx, float* const* y_all, int world, int rank, int row_offset,
                          int in, int out_local, void* stream);
+/* The sharded form of the grouped and fused launches: n <= 4 matrices of one format and column count share x; this
+ * rank keeps rows [row_offset[i], row_offset[i] + out_local[i]) of matrix i resident, and y_all[i * world + r] is rank
+ * r's vector for output i as addressable from this process (world == 1: the local vectors). mode 0: y_i = W_i x
+ * (Q|K|V); mode 1: n == 2, gate | up, the one output is h = silu(W_0 x) * (W_1 x) in the vectors of output 1 (those
+ * of output 0 may be NULL), so only h crosses NVLink. dresidual (n == 1, may be NULL) is a whole-length
+ * vector indexed like the outputs; this rank adds its own rows of it before storing them. Ordering between ranks as for
+ * wv_matvec_dev_gather. */
+int wv_matvec_dev_group_gather(const uint64_t* keys, int n, const float* dx, float* const* y_all, int world, int rank,
+                               const int* row_offset, int in, const int* out_local, int mode, const float* dresidual, void* stream);
 /* Plumbing for the vectors above (cudaMalloc + cudaIpcGetMemHandle / cudaIpcOpenMemHandle with lazy peer
  * access): allocate an exportable device buffer and its 64-byte handle; map a peer's handle; unmap; free. */
 int wv_gather_alloc(size_t bytes, void** dptr, unsigned char handle[64]);

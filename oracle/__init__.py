@@ -232,3 +232,45 @@ def activate(v: np.ndarray, act: int) -> np.ndarray:
     L.wvo_activate.argtypes = [C.c_double, C.c_int, C.POINTER(C.c_int)]
     a = np.asarray(v, np.float64).reshape(-1)
     return np.array([L.wvo_activate(float(t), int(act), None) for t in a], np.float64).reshape(np.shape(v))
+
+
+def rmsnorm(x: np.ndarray, gamma: np.ndarray, eps: float = 1e-5) -> np.ndarray:
+    """rmsnorm.Forward post output for float32 rows (layers/rmsnorm/cpu.go:32-90)."""
+    x = np.ascontiguousarray(x, np.float32)
+    g = np.ascontiguousarray(gamma, np.float32)
+    x2 = x.reshape(-1, g.size)
+    y = np.zeros_like(x2)
+    lib().wvo_rmsnorm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_double]
+    lib().wvo_rmsnorm(x2.ctypes.data, g.ctypes.data, None, y.ctypes.data, x2.shape[0], g.size, float(eps))
+    return y.reshape(x.shape)
+
+
+def rope(vec: np.ndarray, pos: int, num_heads: int, head_dim: int, theta: float = 10000.0) -> np.ndarray:
+    """applyRoPE (layers/mha/rope.go:6-21) on a float64 copy of vec."""
+    v = np.array(vec, np.float64).reshape(-1).copy()
+    lib().wvo_rope.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_double]
+    lib().wvo_rope(v.ctypes.data, int(pos), int(num_heads), int(head_dim), float(theta))
+    return v
+
+
+def attn_decode(q, cache_k, cache_v, num_heads, num_kv_heads, head_dim, kv_len, msl, scale=None) -> np.ndarray:
+    """attnForward for one query token under the causal mask (layers/mha/attn.go:15-120), float64."""
+    q = np.ascontiguousarray(q, np.float64).reshape(-1)
+    ck = np.ascontiguousarray(cache_k, np.float64)
+    cv = np.ascontiguousarray(cache_v, np.float64)
+    out = np.zeros(num_heads * head_dim, np.float64)
+    if scale is None:
+        scale = 1.0 / np.sqrt(head_dim)
+    lib().wvo_attn_decode.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_double]
+    lib().wvo_attn_decode(q.ctypes.data, ck.ctypes.data, cv.ctypes.data, out.ctypes.data, num_heads, num_kv_heads, head_dim, kv_len, msl, float(scale))
+    return out
+
+
+def silu_mul(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+    """simd.SiluMulF32 (simd/silu.go:7-27)."""
+    g = np.ascontiguousarray(gate, np.float32).reshape(-1)
+    u = np.ascontiguousarray(up, np.float32).reshape(-1)
+    out = np.zeros_like(g)
+    lib().wvo_silu_mul.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
+    lib().wvo_silu_mul(g.ctypes.data, u.ctypes.data, out.ctypes.data, g.size)
+    return out

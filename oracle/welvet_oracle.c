@@ -1312,3 +1312,77 @@ double wvo_activate(double x, int act, int *known) {
   if (known) *known = 0;
   return x;
 }
+
+/* ---------- decode steps between the projections (host float64 arithmetic of the reference) ---------- */
+
+/* rmsnorm.forwardHost, scalar arm, T = float32 (layers/rmsnorm/cpu.go:76-85): per token row
+ * inv = 1 / sqrt(sum(x^2) / dim + eps); xhat = x * inv; y = xhat * gamma, each cast to float32. */
+void wvo_rmsnorm(const float *x, const float *gamma, float *xhat, float *y, int ntok, int dim, double eps) {
+  for (int t = 0; t < ntok; t++) {
+    const float *row = x + (size_t)t * dim;
+    double sum_sq = 0;
+    for (int i = 0; i < dim; i++) { double v = (double)row[i]; sum_sq += v * v; }
+    double inv = 1.0 / sqrt(sum_sq / (double)dim + eps);
+    for (int i = 0; i < dim; i++) {
+      double xh = (double)row[i] * inv;
+      if (xhat) xhat[(size_t)t * dim + i] = (float)xh;
+      y[(size_t)t * dim + i] = (float)(xh * (double)gamma[i]);
+    }
+  }
+}
+
+/* applyRoPE (layers/mha/rope.go:6-21): rotates pairs (d, d + headDim/2) in place. */
+void wvo_rope(double *vec, int pos, int num_heads, int head_dim, double theta) {
+  int half = head_dim / 2;
+  if (half <= 0 || theta <= 0) return;
+  for (int h = 0; h < num_heads; h++) {
+    int base = h * head_dim;
+    for (int d = 0; d < half; d++) {
+      double angle = (double)pos / pow(theta, (double)(2 * d) / (double)head_dim);
+      double c = cos(angle), s = sin(angle);
+      double v0 = vec[base + d], v1 = vec[base + d + half];
+      vec[base + d] = v0 * c - v1 * s;
+      vec[base + d + half] = v0 * s + v1 * c;
+    }
+  }
+}
+
+/* attnForward (layers/mha/attn.go:15-120) for seqLen 1, standard softmax, every cache position
+ * 0 .. kvLen-1 allowed (the causal mask for the query at position kvLen-1), no ALiBi, no dropout.
+ * Q [numHeads*headDim]; cacheK / cacheV [msl][numKVHeads*headDim], position p in row p % msl. */
+void wvo_attn_decode(const double *q, const double *cache_k, const double *cache_v, double *out, int num_heads,
+                     int num_kv_heads, int head_dim, int kv_len, int msl, double scale) {
+  int heads_per_kv = num_heads / num_kv_heads, kv_dim = num_kv_heads * head_dim;
+  double *scores = (double *)malloc(sizeof(double) * (size_t)(kv_len > 0 ? kv_len : 1));
+  for (int h = 0; h < num_heads; h++) {
+    int kv_head = h / heads_per_kv, q_off = h * head_dim;
+    double max_score = -1e9;
+    for (int kp = 0; kp < kv_len; kp++) {
+      size_t kb = (size_t)(kp % msl) * kv_dim + (size_t)kv_head * head_dim;
+      double dot = 0;
+      for (int d = 0; d < head_dim; d++) dot += q[q_off + d] * cache_k[kb + d];
+      double score = dot * scale;
+      scores[kp] = score;
+      if (score > max_score) max_score = score;
+    }
+    if (kv_len == 0) { for (int d = 0; d < head_dim; d++) out[q_off + d] = 0; continue; }
+    double exp_sum = 0;
+    for (int i = 0; i < kv_len; i++) { scores[i] = exp(scores[i] - max_score); exp_sum += scores[i]; }
+    double inv = 1.0 / exp_sum;
+    for (int i = 0; i < kv_len; i++) scores[i] *= inv;
+    for (int d = 0; d < head_dim; d++) {
+      double sum = 0;
+      for (int kp = 0; kp < kv_len; kp++) sum += scores[kp] * cache_v[(size_t)(kp % msl) * kv_dim + (size_t)kv_head * head_dim + d];
+      out[q_off + d] = sum;
+    }
+  }
+  free(scores);
+}
+
+/* simd.SiluMulF32 (simd/silu.go:14-27): out[i] = float32(g / (1 + exp(-g)) * up[i]), g = float64(gate[i]). */
+void wvo_silu_mul(const float *gate, const float *up, float *out, int n) {
+  for (int i = 0; i < n; i++) {
+    double g = (double)gate[i];
+    out[i] = (float)(g / (1 + exp(-g)) * (double)up[i]);
+  }
+}

@@ -19,6 +19,8 @@ SYMBOLS = [
     "wv_blob_info", "wv_matvec", "wv_matvec_dev", "wv_unpack", "wv_unpack_dev",
     "wv_pack_sizes", "wv_pack", "wv_pack_upload_dev", "wv_device_status", "wv_matvec_dev_static",
     "wv_argmax_dev", "wv_argmax", "wv_matvec_dev_multi", "wv_matvec_dev_gather", "wv_gather_alloc", "wv_gather_open", "wv_gather_close", "wv_gather_free", "wv_gather_read", "wv_gather_signal", "wv_gather_wait",
+    "wv_matvec_dev_swiglu", "wv_matvec_dev_add", "wv_matvec_dev_group_gather", "wv_rmsnorm_dev", "wv_rope_cache_dev",
+    "wv_attn_decode_dev", "wv_silu_mul_dev", "wv_residual_add_dev",
 ]
 
 # Development hooks (csrc/wv_dev_hooks.h): exported for tests and tuning runs, not part of the public header.
@@ -83,6 +85,14 @@ def lib() -> C.CDLL:
         L.wv_gather_signal.argtypes = [C.POINTER(vp), i, i, vp]
         L.wv_gather_wait.argtypes = [vp, i, vp]
         L.wv_gather_read.argtypes = [vp, sz, vp, sz, vp]
+        L.wv_matvec_dev_swiglu.argtypes = [u64, u64, vp, vp, i, i, vp]
+        L.wv_matvec_dev_add.argtypes = [u64, vp, vp, vp, i, i, vp]
+        L.wv_matvec_dev_group_gather.argtypes = [C.POINTER(u64), i, vp, C.POINTER(vp), i, i, C.POINTER(i), i, C.POINTER(i), i, vp, vp]
+        L.wv_rmsnorm_dev.argtypes = [vp, vp, vp, i, i, C.c_double, vp]
+        L.wv_rope_cache_dev.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, C.c_double, vp]
+        L.wv_attn_decode_dev.argtypes = [vp, vp, vp, vp, i, i, i, i, i, C.c_float, vp]
+        L.wv_silu_mul_dev.argtypes = [vp, vp, vp, i, vp]
+        L.wv_residual_add_dev.argtypes = [vp, vp, i, vp]
         L.wv_unpack.argtypes = [u64, vp]
         L.wv_unpack_dev.argtypes = [u64, vp, vp]
         L.wv_pack_sizes.argtypes = [i, i, i, i, i, C.POINTER(sz), C.POINTER(sz), C.POINTER(sz)]

@@ -26,6 +26,7 @@ SOURCES = {
     "wv_gemv.cu": [],
     "wv_gemv_tma.cu": [],
     "wv_gemv_mma.cu": [],
+    "wv_decode.cu": [],
     "wv_api.cu": [],
 }
 
@@ -54,7 +55,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= _newest_dep():
         return LIB
     os.makedirs(OBJ, exist_ok=True)
-    with ThreadPoolExecutor(max_workers=6) as ex:
+    with ThreadPoolExecutor(max_workers=7) as ex:
         objs = list(ex.map(lambda kv: _compile(kv[0], kv[1], verbose), SOURCES.items()))
     cmd = ["nvcc", *ARCH, "-shared", "-cudart", "static", "-o", LIB, *objs]
     res = subprocess.run(cmd, capture_output=True, text=True)

@@ -495,6 +495,152 @@ extern "C" int wv_matvec_dev_gather(uint64_t key, const float* dx, float* const*
   return rc;
 }
 
+// ---------------------------------------------------------------- fused projection epilogues and decode steps
+int wv_launch_rmsnorm(const float* dx, const float* dgamma, float* dy, int rows, int dim, double eps, cudaStream_t st);   // wv_decode.cu
+int wv_launch_rope_cache(float* dq, const float* dk, const float* dv, float* dcache_k, float* dcache_v, int pos, int msl,
+                         int num_heads, int num_kv_heads, int head_dim, double theta, cudaStream_t st);
+int wv_launch_attn_decode(const float* dq, const float* dcache_k, const float* dcache_v, float* dout, int num_heads, int num_kv_heads,
+                          int head_dim, int kv_len, int msl, float scale, cudaStream_t st);
+int wv_launch_silu_mul(const float* dgate, const float* dup, float* dout, int n, cudaStream_t st);
+int wv_launch_residual_add(float* ddst, const float* dadd, int n, cudaStream_t st);
+
+// Sharded or local group launch with fused epilogues. keys[n]; y_all[n * world] lists, matrix by matrix, every
+// rank's output vector (world == 1: just the local ones); row_offset[n] is where this rank's rows start in them.
+static int fused_launch(const char* who, const uint64_t* keys, int n, const float* dx, float* const* y_all, int world, int rank,
+                        const int* row_offset, int in, const int* out_local, int mode, const float* dres, cudaStream_t st) {
+  if (!keys || !dx || !y_all || !out_local || n < 1 || n > 4) { wv_set_error("%s: bad argument (1..4 matrices)", who); return WV_EARG; }
+  if (world < 1 || world > WV_MAX_PEERS || rank < 0 || rank >= world) { wv_set_error("%s: world=%d rank=%d (at most %d ranks)", who, world, rank, WV_MAX_PEERS); return WV_EARG; }
+  if (mode == 1 && n != 2) { wv_set_error("%s: the gate product takes exactly two matrices", who); return WV_EARG; }
+  if (dres && n != 1) { wv_set_error("%s: a residual goes with one matrix", who); return WV_EARG; }
+  WvDevBlob blobs[4];
+  int rc;
+  for (int i = 0; i < n; i++) {
+    Entry e;
+    if ((rc = lookup(keys[i], &e))) return rc;
+    if ((rc = check_dims(e, 1, in, out_local[i]))) return rc;
+    blobs[i] = e.blob;
+    for (int q = 0; q < world; q++)
+      if (!y_all[i * world + q] && !(mode == 1 && i == 0)) { wv_set_error("%s: output %d of rank %d is null", who, i, q); return WV_EARG; }
+  }
+  if (mode == 1 && blobs[0].rows != blobs[1].rows) { wv_set_error("%s: gate and up differ in rows", who); return WV_ESHAPE; }
+  WvFuse fuse{};
+  fuse.mode = mode;
+  fuse.residual = dres ? dres + (row_offset ? row_offset[0] : 0) : nullptr;   // indexed like the output vectors
+  fuse.npeers = world > 1 ? world : 0;
+  float* local[4];
+  for (int i = 0; i < n; i++) {
+    const int off = row_offset ? row_offset[i] : 0;
+    float* own = y_all[i * world + rank];
+    local[i] = own ? own + off : nullptr;
+    for (int q = 0; q < world; q++) fuse.py[i][q] = y_all[i * world + q] ? y_all[i * world + q] + off : nullptr;
+  }
+  const bool need_fuse = mode != 0 || dres || world > 1;
+  if (blobs[0].fast && blobs[0].format != WV_NONE) {
+    wv_cur_fuse = need_fuse ? &fuse : nullptr;
+    rc = wv_launch_gemv_tma_group(blobs, n, dx, local, 1, 0, 0, st);
+    wv_cur_fuse = nullptr;
+    if (rc != 1) {
+      if (rc) wv_set_error("%s: launch failed (%d): %s", who, rc, cudaGetErrorString(cudaGetLastError()));
+      return rc;
+    }
+  }
+  // Shapes or mixes the grouped kernel does not take: the same results from separate launches.
+  if (world > 1) {
+    if (mode != 0 || dres) { wv_set_error("%s: this shape has no sharded fused path", who); return WV_ESHAPE; }
+    for (int i = 0; i < n; i++) {
+      WvPeers peers{};
+      peers.n = world; peers.self = rank;
+      for (int q = 0; q < world; q++) peers.y[q] = fuse.py[i][q];
+      wv_cur_peers = &peers;
+      rc = wv_launch_gemv(blobs[i], dx, peers.y[rank], 1, 0, blobs[i].rows, st);
+      wv_cur_peers = nullptr;
+      if (rc) return rc;
+    }
+    return WV_OK;
+  }
+  if (mode == 1) {
+    // gate into the output vector, up into a scratch slot, then the product in place
+    float* up = reinterpret_cast<float*>(wv_scratch_take((size_t)blobs[1].rows * 4));
+    if (!up) { wv_set_error("%s: activation scratch too small", who); return WV_ENOMEM; }
+    if ((rc = wv_launch_gemv(blobs[0], dx, local[1], 1, 0, blobs[0].rows, st))) return rc;
+    if ((rc = wv_launch_gemv(blobs[1], dx, up, 1, 0, blobs[1].rows, st))) return rc;
+    return wv_launch_silu_mul(local[1], up, local[1], blobs[1].rows, st);
+  }
+  for (int i = 0; i < n; i++) {
+    if (dres && dres == local[i]) {   // in place: W x into scratch, then added
+      float* tmp = reinterpret_cast<float*>(wv_scratch_take((size_t)blobs[i].rows * 4));
+      if (!tmp) { wv_set_error("%s: activation scratch too small", who); return WV_ENOMEM; }
+      if ((rc = wv_launch_gemv(blobs[i], dx, tmp, 1, 0, blobs[i].rows, st))) return rc;
+      if ((rc = wv_launch_residual_add(local[i], tmp, blobs[i].rows, st))) return rc;
+    } else {
+      if ((rc = wv_launch_gemv(blobs[i], dx, local[i], 1, 0, blobs[i].rows, st))) return rc;
+      if (dres && (rc = wv_launch_residual_add(local[i], dres, blobs[i].rows, st))) return rc;
+    }
+  }
+  return WV_OK;
+}
+
+extern "C" int wv_matvec_dev_swiglu(uint64_t key_gate, uint64_t key_up, const float* dx, float* dh, int in, int out, void* stream) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!dh) { wv_set_error("wv_matvec_dev_swiglu: null output"); return WV_EARG; }
+  const uint64_t keys[2] = {key_gate, key_up};
+  float* ys[2] = {nullptr, dh};
+  const int outs[2] = {out, out};
+  return fused_launch("wv_matvec_dev_swiglu", keys, 2, dx, ys, 1, 0, nullptr, in, outs, 1, nullptr, static_cast<cudaStream_t>(stream));
+}
+extern "C" int wv_matvec_dev_add(uint64_t key, const float* dx, const float* dresidual, float* dy, int in, int out, void* stream) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!dy || !dresidual) { wv_set_error("wv_matvec_dev_add: null pointer"); return WV_EARG; }
+  float* ys[1] = {dy};
+  return fused_launch("wv_matvec_dev_add", &key, 1, dx, ys, 1, 0, nullptr, in, &out, 0, dresidual, static_cast<cudaStream_t>(stream));
+}
+extern "C" int wv_matvec_dev_group_gather(const uint64_t* keys, int n, const float* dx, float* const* y_all, int world, int rank,
+                                          const int* row_offset, int in, const int* out_local, int mode, const float* dresidual, void* stream) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  return fused_launch("wv_matvec_dev_group_gather", keys, n, dx, y_all, world, rank, row_offset, in, out_local, mode, dresidual,
+                      static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int wv_rmsnorm_dev(const float* dx, const float* dgamma, float* dy, int rows, int dim, double eps, void* stream) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!dx || !dgamma || !dy || rows < 1 || dim < 1) { wv_set_error("wv_rmsnorm_dev: bad argument"); return WV_EARG; }
+  return wv_launch_rmsnorm(dx, dgamma, dy, rows, dim, eps, static_cast<cudaStream_t>(stream));
+}
+extern "C" int wv_rope_cache_dev(float* dq, const float* dk, const float* dv, float* dcache_k, float* dcache_v, int pos, int max_seq_len,
+                                 int num_heads, int num_kv_heads, int head_dim, double theta, void* stream) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!dq || !dk || !dv || !dcache_k || !dcache_v || pos < 0 || max_seq_len < 1 || num_heads < 1 || num_kv_heads < 1 || head_dim < 2 || (head_dim & 1)) {
+    wv_set_error("wv_rope_cache_dev: bad argument"); return WV_EARG;
+  }
+  return wv_launch_rope_cache(dq, dk, dv, dcache_k, dcache_v, pos, max_seq_len, num_heads, num_kv_heads, head_dim, theta, static_cast<cudaStream_t>(stream));
+}
+extern "C" int wv_attn_decode_dev(const float* dq, const float* dcache_k, const float* dcache_v, float* dout, int num_heads, int num_kv_heads,
+                                  int head_dim, int kv_len, int max_seq_len, float scale, void* stream) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!dq || !dcache_k || !dcache_v || !dout || num_heads < 1 || num_kv_heads < 1 || kv_len < 1 || max_seq_len < 1 || kv_len > max_seq_len) {
+    wv_set_error("wv_attn_decode_dev: bad argument"); return WV_EARG;
+  }
+  return wv_launch_attn_decode(dq, dcache_k, dcache_v, dout, num_heads, num_kv_heads, head_dim, kv_len, max_seq_len, scale, static_cast<cudaStream_t>(stream));
+}
+extern "C" int wv_silu_mul_dev(const float* dgate, const float* dup, float* dout, int n, void* stream) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!dgate || !dup || !dout || n < 0) { wv_set_error("wv_silu_mul_dev: bad argument"); return WV_EARG; }
+  return wv_launch_silu_mul(dgate, dup, dout, n, static_cast<cudaStream_t>(stream));
+}
+extern "C" int wv_residual_add_dev(float* ddst, const float* dadd, int n, void* stream) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!ddst || !dadd || n < 0) { wv_set_error("wv_residual_add_dev: bad argument"); return WV_EARG; }
+  return wv_launch_residual_add(ddst, dadd, n, static_cast<cudaStream_t>(stream));
+}
+
 int wv_launch_gather_signal(unsigned* const* flags_all, int world, int rank, cudaStream_t st);   // wv_gemv.cu
 int wv_launch_gather_wait(unsigned* flags_own, int world, cudaStream_t st);
 

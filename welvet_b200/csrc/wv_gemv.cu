@@ -563,6 +563,7 @@ int wv_launch_argmax(const float* d_logits, int n, int* d_out, cudaStream_t st) 
 }
 
 thread_local const WvPeers* wv_cur_peers = nullptr;
+thread_local const WvFuse* wv_cur_fuse = nullptr;
 
 // Copies n floats of this GPU's slice to the same position of every other rank's vector (the
 // kernels without a peer-storing epilogue finish with this).

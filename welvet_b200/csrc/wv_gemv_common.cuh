@@ -494,6 +494,16 @@ struct WvPeers {
 // Set by wv_matvec_dev_gather around its launch (wv_api.cu); the bulk-copy kernels pass it on.
 extern thread_local const WvPeers* wv_cur_peers;
 
+// Fused epilogues of the grouped bulk-copy launch, set by the fused entry points around their launch:
+// the SwiGLU gate product, a residual add, and per-matrix output vectors on every rank.
+struct WvFuse {
+  int mode;                 // 0: y_i = W_i x;  1: h = silu(W_0 x) * (W_1 x), stored as output 1
+  const float* residual;    // one matrix: y = W x + residual
+  int npeers;               // > 0: rows go to py[matrix][rank] (own and peers' vectors, already offset to this rank's rows)
+  float* py[4][WV_MAX_PEERS];
+};
+extern thread_local const WvFuse* wv_cur_fuse;
+
 // wv_gemv.cu
 uint4* wv_scratch_take(size_t bytes);
 int wv_launch_xquant(int bits_lo, const float* dx, int cols, int batch, int imid, uint4* out, cudaStream_t st);

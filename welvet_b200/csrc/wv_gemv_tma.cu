@@ -41,12 +41,14 @@ struct TmaGeom {
   int force3;        // development switch: always use the 24-bit activation records
   unsigned x_off;    // staged activations: 33 floats per chunk (32 + one of padding)
   unsigned red_off;  // float red[2][nrg][nwc][32]
+  unsigned gate_off; // gate | up launches: the gate's row sums of this CTA's band (TMA_GATE_ROWS floats)
   unsigned bar_off;  // full[nstage], empty[nstage]
 };
 
 // The matrices one launch works through (same format, columns and group; they share x): the
 // planes, output vector and row split of each. A plain GEMV is a group of one.
 #define TMA_MAX_GROUP 4
+#define TMA_GATE_ROWS 512
 struct TmaGroup {
   int n;
   int rows[TMA_MAX_GROUP];
@@ -59,7 +61,10 @@ struct TmaGroup {
 // without it: the extra parameters and loop nest cost 0.3-0.6 us per launch when they were always there.
 struct TmaExt {
   TmaGroup grp;
-  WvPeers peers;
+  int mode;                 // 0: y_i = W_i x;  1: matrices 0 | 1 are gate | up and the one output is silu(W_0 x) * (W_1 x)
+  int npeers;               // > 0: every output row goes to all ranks' vectors py[matrix][rank] instead of grp.y[matrix]
+  const float* residual;    // single matrix: added to each row sum before the store (may alias the output)
+  float* py[TMA_MAX_GROUP][WV_MAX_PEERS];
 };
 struct TmaNoExt {};
 template <bool EXT> struct TmaExtArgs { using type = TmaNoExt; };
@@ -142,7 +147,6 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int s_abort;
   __shared__ unsigned s_xissued;   // consumer warps that have issued their loads of x
-  __shared__ float2 s_stat[TMA_MAX_ROW_GROUPS][TMA_CONSUMER_WARPS];   // per column warp: {sum of chunk maxima, sum |x|}
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   // band of this CTA in matrix i, without divisions: the host splits the rows as evenly as possible
   const int bid = blockIdx.x;
@@ -290,6 +294,7 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   int par = 0;
   bool dead = false;
   int nslots = 0;
+  int cur_mat = 0;   // matrix of the group being worked on
   auto flush = [&](int batch_base) {
     float* mine = red + (((size_t)par * g.nrg + rg) * g.nwc + wc) * 32;
     mine[lane] = keep;
@@ -301,14 +306,27 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
       const int n = batch_base + lane;
       const int row = c_lo + (n / RT) * g.tr + rg * RT + (n % RT);
       if (n < nslots && (n / RT) * g.tr + rg * RT + (n % RT) < band && rg * RT + (n % RT) < g.tr) {
-        bool stored = false;
         if constexpr (EXT) {
-          if (ext.peers.n) {
-            for (int q = 0; q < ext.peers.n; q++) ext.peers.y[q][row_begin + row] = sum;   // own and peers' copies of y
-            stored = true;
+          bool skip = false;
+          if (ext.mode == 1) {
+            // SwiGLU gate product (simd/silu.go:14-27) in the epilogue: this thread owns the same row of the
+            // gate matrix and of the up matrix, so the gate's sum waits in shared memory for the up row
+            float* sg = reinterpret_cast<float*>(smem + g.gate_off);
+            const int rib = (n / RT) * g.tr + rg * RT + (n % RT);
+            if (cur_mat == 0) { sg[rib] = sum; skip = true; }
+            else { const double gt = (double)sg[rib]; sum = (float)(gt / (1.0 + exp(-gt)) * (double)sum); }
           }
+          if (!skip) {
+            if (ext.residual) sum += ext.residual[(size_t)blockIdx.y * ext.grp.rows[cur_mat] + row_begin + row];
+            if (ext.npeers) {
+              for (int q = 0; q < ext.npeers; q++) ext.py[cur_mat][q][row_begin + row] = sum;   // own and peers' copies of y
+            } else {
+              yb[row] = sum;
+            }
+          }
+        } else {
+          yb[row] = sum;
         }
-        if (!stored) yb[row] = sum;
       }
     }
     par ^= 1;
@@ -360,6 +378,7 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   auto main_loop = [&](auto dot) {
     for (int bi = 0; bi < nmat; bi++) {   // one matrix after the other; ring position and x registers carry over
       set_band(bi);
+      cur_mat = bi;
       nslots = ntiles * RT;
       if constexpr (EXT) yb = ext.grp.y[bi] + (size_t)blockIdx.y * ext.grp.rows[bi] + row_begin;
       else yb = y + (size_t)blockIdx.y * b.rows + row_begin;
@@ -472,10 +491,13 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
     float ta = amax, ts = asum;
 #pragma unroll
     for (int o = 16; o; o >>= 1) { ta += __shfl_xor_sync(0xffffffffu, ta, o); ts += __shfl_xor_sync(0xffffffffu, ts, o); }
-    if (lane == 0) s_stat[rg][wc] = make_float2(ta, ts);
+    // per column warp {sum of chunk maxima, sum |x|}: kept in the second half of the row-sum exchange area, which
+    // the row group writes only after its first flush barrier, i.e. after all its warps have read these
+    float2* stat = reinterpret_cast<float2*>(red + (size_t)g.nrg * g.nwc * 32) + (size_t)rg * g.nwc;
+    if (lane == 0) stat[wc] = make_float2(ta, ts);
     asm volatile("bar.sync %0, %1;" ::"r"(rg + 1), "r"(g.nwc * 32) : "memory");
     ta = 0.f; ts = 0.f;
-    for (int q = 0; q < g.nwc; q++) { const float2 p = s_stat[rg][q]; ta += p.x; ts += p.y; }
+    for (int q = 0; q < g.nwc; q++) { const float2 p = stat[q]; ta += p.x; ts += p.y; }
     const bool wide = !(ta <= 0.25f * ts) || g.force3;   // NaN compares false: non-finite input takes the wide path
     if (!wide) {
       XQRegs2 xr;
@@ -577,7 +599,10 @@ static int launch_tma(const WvDevBlob* bl, int nb, const float* dx, float* const
   for (int i = 0; i < 5; i++) { g.off[i] = off; off = align128(off + g.rb[i] * g.tr); }
   g.stage_bytes = off;
   const unsigned xbytes = align128((unsigned)g.cpr * 132u);
-  const unsigned fixed = xbytes + align128(2u * g.nrg * g.nwc * 32 * 4 + (fi.table ? 4096u : 0u)) + 2 * TMA_MAX_STAGES * 8 + 128;
+  const WvFuse* fuse = wv_cur_fuse;
+  const bool gated = fuse && fuse->mode == 1;
+  const unsigned gate_bytes = gated ? TMA_GATE_ROWS * 4u : 0u;
+  const unsigned fixed = xbytes + align128(2u * g.nrg * g.nwc * 32 * 4 + (fi.table ? 4096u : 0u)) + gate_bytes + 2 * TMA_MAX_STAGES * 8 + 128;
   const unsigned avail = 225u * 1024u;  // 227 KB per CTA minus static shared memory and slack
   if (g.stage_bytes * 2 + fixed > avail) return 1;
   int ns = (int)((avail - fixed) / g.stage_bytes);
@@ -588,7 +613,8 @@ static int launch_tma(const WvDevBlob* bl, int nb, const float* dx, float* const
   g.nstage = ns;
   g.x_off = g.stage_bytes * ns;
   g.red_off = g.x_off + xbytes;
-  g.bar_off = align128(g.red_off + 2u * g.nrg * g.nwc * 32 * 4 + (fi.table ? 4096u : 0u));
+  g.gate_off = align128(g.red_off + 2u * g.nrg * g.nwc * 32 * 4 + (fi.table ? 4096u : 0u));
+  g.bar_off = g.gate_off + gate_bytes;
   const size_t smem = g.bar_off + 2 * TMA_MAX_STAGES * 8;
 
   int grid = wv_sm_count();
@@ -598,7 +624,11 @@ static int launch_tma(const WvDevBlob* bl, int nb, const float* dx, float* const
   const uint4* xq = nullptr;  // activations are quantised inside the kernel
   int dev = 0; cudaGetDevice(&dev);
   cudaError_t e;
-  if (nb == 1 && !wv_cur_peers) {
+  if (gated) {
+    if (nb != 2 || bl[0].rows != bl[1].rows || batch != 1) return WV_ESHAPE;
+    if (bl[0].rows / grid + 1 > TMA_GATE_ROWS) return 1;
+  }
+  if (nb == 1 && !wv_cur_peers && !fuse) {
     auto kern = gemv_tma_kernel<F, RT, PF, false>;
     static unsigned attr_mask = 0;
     if (!(attr_mask & (1u << dev))) {
@@ -624,7 +654,21 @@ static int launch_tma(const WvDevBlob* bl, int nb, const float* dx, float* const
         ext.grp.plane[i][0] = bl[i].lo; ext.grp.plane[i][1] = bl[i].hi; ext.grp.plane[i][2] = bl[i].p0; ext.grp.plane[i][3] = bl[i].p1; ext.grp.plane[i][4] = bl[i].km;
         ext.grp.y[i] = dys[i];
       }
-      if (wv_cur_peers) { if (batch != 1 || nb != 1) return WV_ESHAPE; ext.peers = *wv_cur_peers; }
+      if (wv_cur_peers) {
+        if (batch != 1 || nb != 1) return WV_ESHAPE;
+        ext.npeers = wv_cur_peers->n;
+        for (int q = 0; q < ext.npeers; q++) ext.py[0][q] = wv_cur_peers->y[q];
+      }
+      if (fuse) {
+        ext.mode = fuse->mode;
+        ext.residual = fuse->residual;
+        if (fuse->residual && nb != 1) return WV_ESHAPE;
+        if (fuse->npeers) {
+          if (batch != 1) return WV_ESHAPE;
+          ext.npeers = fuse->npeers;
+          for (int i = 0; i < nb; i++) for (int q = 0; q < ext.npeers; q++) ext.py[i][q] = fuse->py[i][q];
+        }
+      }
       e = launch_pdl(kern, dim3(grid, batch), dim3(TMA_THREADS), smem, st, b, xq, dx, dys[0], rb_, re, g, g_err_dev, ext);
     } else {
       return 1;
@@ -656,6 +700,10 @@ int wv_launch_gemv_tma(const WvDevBlob& b, const float* dx, float* dy, int batch
   // kernel (one column segment per 16-row block; measured 3-10 % faster there, level or slower on
   // wider rows and for IQ3_XXS). Tuning codes 21, 22, 24 force it with that many chunk pairs per
   // warp; any other non-zero code keeps everything on the dp4a kernel.
+  if (wv_cur_fuse) {   // fused epilogues live in the grouped instance of the dp4a kernel
+    float* dys1[1] = {dy};
+    return wv_launch_gemv_tma_group(&b, 1, dx, dys1, batch, row_begin, row_end, st);
+  }
   if (g_tma_rt >= 20 || (g_tma_rt == 0 && b.cols <= 4096 && b.format != WV_IQ3_XXS)) {
     const int rc = wv_launch_gemv_mma(b, dx, dy, batch, row_begin, row_end, st, g_tma_rt >= 20 ? g_tma_rt - 20 : 4);
     if (rc != 1) return rc;

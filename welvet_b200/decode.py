@@ -1,0 +1,93 @@
+"""Single-token decode of one decoder block with every step on the device: the reference's
+block walk (model/transformer/forward.go:57-76: RMSNorm -> attention -> residual -> RMSNorm ->
+SwiGLU -> residual) with its host-side float64 steps (layers/rmsnorm/cpu.go, layers/mha/cpu.go,
+layers/mha/rope.go, layers/mha/attn.go, layers/swiglu/cpu.go) replaced by the device entries of
+include/welvet_cuda.h, so that activations stay in HBM between the projection GEMVs.
+
+All pointers are device addresses (ints); the caller owns the buffers (for example torch tensors)."""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+from . import quant
+from ._lib import check, lib
+
+
+def RMSNormCUDA(dx: int, dgamma: int, dy: int, rows: int, dim: int, eps: float, stream: int = 0) -> None:
+    """rmsnorm.Forward post output (layers/rmsnorm/cpu.go:32-90) for float32 rows."""
+    check(lib().wv_rmsnorm_dev(dx, dgamma, dy, rows, dim, eps, stream))
+
+
+def RoPECacheCUDA(dq: int, dk: int, dv: int, dcache_k: int, dcache_v: int, pos: int, max_seq_len: int, num_heads: int,
+                  num_kv_heads: int, head_dim: int, theta: float, stream: int = 0) -> None:
+    """applyRoPE on Q (in place) and K, K and V into cache row pos % max_seq_len (mha/rope.go:6-21, mha/cpu.go:184-207)."""
+    check(lib().wv_rope_cache_dev(dq, dk, dv, dcache_k, dcache_v, pos, max_seq_len, num_heads, num_kv_heads, head_dim, theta, stream))
+
+
+def AttnDecodeCUDA(dq: int, dcache_k: int, dcache_v: int, dout: int, num_heads: int, num_kv_heads: int, head_dim: int, kv_len: int,
+                   max_seq_len: int, scale: float, stream: int = 0) -> None:
+    """attnForward for one query token under the causal mask (mha/attn.go:15-120)."""
+    check(lib().wv_attn_decode_dev(dq, dcache_k, dcache_v, dout, num_heads, num_kv_heads, head_dim, kv_len, max_seq_len, scale, stream))
+
+
+def SiluMulCUDA(dgate: int, dup: int, dout: int, n: int, stream: int = 0) -> None:
+    """simd.SiluMulF32 (simd/silu.go:7-27)."""
+    check(lib().wv_silu_mul_dev(dgate, dup, dout, n, stream))
+
+
+def ResidualAddCUDA(ddst: int, dadd: int, n: int, stream: int = 0) -> None:
+    """residualAddInPlace (model/transformer/scratch.go:33-41)."""
+    check(lib().wv_residual_add_dev(ddst, dadd, n, stream))
+
+
+def MatVecSwiGLUCUDA(key_gate: int, key_up: int, dx: int, dh: int, in_: int, out: int, stream: int = 0) -> None:
+    """h = silu(W_gate x) * (W_up x) in one launch (swiglu/cpu.go:29-52, fusedgpu/shaders.go:159-222)."""
+    check(lib().wv_matvec_dev_swiglu(key_gate, key_up, dx, dh, in_, out, stream))
+
+
+def MatVecAddCUDA(key: int, dx: int, dresidual: int, dy: int, in_: int, out: int, stream: int = 0) -> None:
+    """y = W x + residual in one launch (forward.go:65,75; fusedgpu/hybrid_shaders.go:82)."""
+    check(lib().wv_matvec_dev_add(key, dx, dresidual, dy, in_, out, stream))
+
+
+@dataclass
+class BlockConfig:
+    """Shape of one decoder block (mha.Config / swiglu.Config fields the decode path uses)."""
+    DModel: int
+    NumHeads: int
+    NumKVHeads: int
+    HeadDim: int
+    IntermediateDim: int
+    MaxSeqLen: int
+    Eps: float = 1e-5
+    RoPETheta: float = 10000.0
+
+
+class BlockDecoder:
+    """One block's single-token decode as eight launches: RMSNorm, Q|K|V group, RoPE + cache write,
+    attention, O + residual, RMSNorm, gate|up with the SiLU product, down + residual. `keys` maps
+    q, k, v, o, gate, up, down to resident blob keys; `bufs` maps the working vectors (n1, q, k, v,
+    attn, n2, ffn) and the weights attn_norm / ffn_norm and caches cache_k / cache_v to device pointers."""
+
+    def __init__(self, cfg: BlockConfig, keys: dict, bufs: dict):
+        self.cfg, self.keys, self.bufs = cfg, keys, bufs
+        c = cfg
+        self._qkv_keys = (C.c_uint64 * 3)(keys["q"], keys["k"], keys["v"])
+        self._qkv_outs = (C.c_int * 3)(c.NumHeads * c.HeadDim, c.NumKVHeads * c.HeadDim, c.NumKVHeads * c.HeadDim)
+        self._qkv_ptrs = (C.c_void_p * 3)(bufs["q"], bufs["k"], bufs["v"])
+
+    def step(self, dh: int, pos: int, stream: int = 0) -> None:
+        """h (device pointer to DModel floats) is updated in place; pos is the token's position."""
+        c, k, b, L = self.cfg, self.keys, self.bufs, lib()
+        qd = c.NumHeads * c.HeadDim
+        RMSNormCUDA(dh, b["attn_norm"], b["n1"], 1, c.DModel, c.Eps, stream)
+        check(L.wv_matvec_dev_multi(self._qkv_keys, 3, b["n1"], self._qkv_ptrs, 1, c.DModel, self._qkv_outs, stream))
+        RoPECacheCUDA(b["q"], b["k"], b["v"], b["cache_k"], b["cache_v"], pos, c.MaxSeqLen, c.NumHeads, c.NumKVHeads, c.HeadDim, c.RoPETheta, stream)
+        AttnDecodeCUDA(b["q"], b["cache_k"], b["cache_v"], b["attn"], c.NumHeads, c.NumKVHeads, c.HeadDim, min(pos + 1, c.MaxSeqLen), c.MaxSeqLen,
+                       1.0 / (c.HeadDim ** 0.5), stream)
+        MatVecAddCUDA(k["o"], b["attn"], dh, dh, qd, c.DModel, stream)
+        RMSNormCUDA(dh, b["ffn_norm"], b["n2"], 1, c.DModel, c.Eps, stream)
+        MatVecSwiGLUCUDA(k["gate"], k["up"], b["n2"], b["ffn"], c.DModel, c.IntermediateDim, stream)
+        MatVecAddCUDA(k["down"], b["ffn"], dh, dh, c.IntermediateDim, c.DModel, stream)
