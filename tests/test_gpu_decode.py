@@ -119,9 +119,10 @@ def test_fused_swiglu_and_residual_epilogues(wv, fmt, shape):
         dg, du = (TOL * O.sum_abs_wx(ob, x) for ob in obs)
         bound = 1.1 * dg * np.abs(u_ref) + np.abs(g_ref) * du + dg * du + 1e-6 * np.abs(want) + 1e-30
         assert np.all(np.abs(h.cpu().numpy().astype(np.float64) - want) <= bound)
-        # the fused product equals the product of the separately computed vectors to float rounding
-        sep = O.silu_mul(gate.cpu().numpy(), up.cpu().numpy())
-        np.testing.assert_allclose(h.cpu().numpy(), sep, rtol=1e-5, atol=1e-6 * float(np.abs(sep).max()))
+        # and agrees with the product of the separately computed vectors within the same budget (the separate launches
+        # may run on another kernel of the family, with its own rounding)
+        sep = O.silu_mul(gate.cpu().numpy(), up.cpu().numpy()).astype(np.float64)
+        assert np.all(np.abs(h.cpu().numpy().astype(np.float64) - sep) <= 2 * bound)
         # projection + residual, out of place and in place
         res = np.random.default_rng(3).normal(0, 1, rows).astype(np.float32)
         dres, y = _dev(res), torch.zeros(rows, device="cuda")

@@ -9,7 +9,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libwelvet_cuda.so")
+LIB_PATH = os.environ.get("WELVET_CUDA_LIB") or os.path.join(_HERE, "libwelvet_cuda.so")   # the variable selects a development build
 
 # Every symbol include/welvet_cuda.h declares.
 SYMBOLS = [

@@ -14,8 +14,10 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-OBJ = os.path.join(HERE, "build")
-LIB = os.path.join(HERE, "libwelvet_cuda.so")
+OBJ = os.path.join(HERE, "build" + os.environ.get("WV_LIB_SUFFIX", ""))
+# WV_LIB_SUFFIX builds a second library beside the product one (development variants, e.g. with -DWV_PHASES)
+_SUFFIX = os.environ.get("WV_LIB_SUFFIX", "")
+LIB = os.path.join(HERE, f"libwelvet_cuda{_SUFFIX}.so")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -27,6 +29,7 @@ SOURCES = {
     "wv_gemv_tma.cu": [],
     "wv_gemv_mma.cu": [],
     "wv_decode.cu": [],
+    "wv_gemv_tc.cu": [],
     "wv_api.cu": [],
 }
 
@@ -55,7 +58,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= _newest_dep():
         return LIB
     os.makedirs(OBJ, exist_ok=True)
-    with ThreadPoolExecutor(max_workers=7) as ex:
+    with ThreadPoolExecutor(max_workers=8) as ex:
         objs = list(ex.map(lambda kv: _compile(kv[0], kv[1], verbose), SOURCES.items()))
     cmd = ["nvcc", *ARCH, "-shared", "-cudart", "static", "-o", LIB, *objs]
     res = subprocess.run(cmd, capture_output=True, text=True)

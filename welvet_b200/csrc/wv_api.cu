@@ -537,7 +537,7 @@ static int fused_launch(const char* who, const uint64_t* keys, int n, const floa
   const bool need_fuse = mode != 0 || dres || world > 1;
   if (blobs[0].fast && blobs[0].format != WV_NONE) {
     wv_cur_fuse = need_fuse ? &fuse : nullptr;
-    rc = wv_launch_gemv_tma_group(blobs, n, dx, local, 1, 0, 0, st);
+    rc = wv_launch_gemv_tma_group(blobs, n, dx, local, 1, 0, n == 1 ? blobs[0].rows : 0, st);   // a single matrix carries its row range
     wv_cur_fuse = nullptr;
     if (rc != 1) {
       if (rc) wv_set_error("%s: launch failed (%d): %s", who, rc, cudaGetErrorString(cudaGetLastError()));

@@ -511,5 +511,7 @@ int wv_sm_count();
 // wv_gemv_tma.cu: returns WV_OK, an error, or 1 when the shape does not fit the TMA kernel
 int wv_launch_gemv_tma(const WvDevBlob& b, const float* dx, float* dy, int batch, int row_begin, int row_end, cudaStream_t st);
 int wv_launch_gemv_tma_group(const WvDevBlob* b, int nb, const float* dx, float* const* dy, int batch, int row_begin, int row_end, cudaStream_t st);
+// wv_gemv_tc.cu: same contract (all packed integer-code formats, tensor-pipe dot products)
+int wv_launch_gemv_tc(const WvDevBlob& b, const float* dx, float* dy, int batch, int row_begin, int row_end, cudaStream_t st);
 // wv_gemv_mma.cu: same contract; pw = chunk pairs per warp per tile (1, 2, 4)
 int wv_launch_gemv_mma(const WvDevBlob& b, const float* dx, float* dy, int batch, int row_begin, int row_end, cudaStream_t st, int pw);

@@ -582,6 +582,7 @@ int wv_tma_tuning_stages() { return g_tma_stages; }
 static int g_act_width = 0;
 extern "C" void wv_set_act_width(int limbs) { g_act_width = limbs; }
 int wv_act_width() { return g_act_width; }
+int wv_tc_prequant() { return g_tma_rt == 31 ? 1 : 0; }
 
 template <int F, int RT, bool PF>
 static int launch_tma(const WvDevBlob* bl, int nb, const float* dx, float* const* dys, int batch, int rb_, int re, cudaStream_t st) {
@@ -704,8 +705,13 @@ int wv_launch_gemv_tma(const WvDevBlob& b, const float* dx, float* dy, int batch
     float* dys1[1] = {dy};
     return wv_launch_gemv_tma_group(&b, 1, dx, dys1, batch, row_begin, row_end, st);
   }
-  if (g_tma_rt >= 20 || (g_tma_rt == 0 && b.cols <= 4096 && b.format != WV_IQ3_XXS)) {
-    const int rc = wv_launch_gemv_mma(b, dx, dy, batch, row_begin, row_end, st, g_tma_rt >= 20 ? g_tma_rt - 20 : 4);
+  // Tuning code 30 routes everything the tensor-pipe kernel of wv_gemv_tc.cu serves through it.
+  if (g_tma_rt == 30 || g_tma_rt == 31) {
+    const int rc = wv_launch_gemv_tc(b, dx, dy, batch, row_begin, row_end, st);
+    if (rc != 1) return rc;
+  }
+  if ((g_tma_rt >= 20 && g_tma_rt < 30) || ((g_tma_rt == 0 || g_tma_rt >= 30) && b.cols <= 4096 && b.format != WV_IQ3_XXS)) {
+    const int rc = wv_launch_gemv_mma(b, dx, dy, batch, row_begin, row_end, st, (g_tma_rt >= 20 && g_tma_rt < 30) ? g_tma_rt - 20 : 4);
     if (rc != 1) return rc;
   } else if (g_tma_rt == 0 && b.format == WV_Q8_0) {
     // 8-bit codes need no unpacking, so the tensor-pipe kernel also wins on wider rows (two chunk pairs per warp
