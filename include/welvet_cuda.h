@@ -133,11 +133,26 @@ int wv_residual_add_dev(float* ddst, const float* dadd, int n, void* stream);
  * wv_argmax synchronises and returns it to the host. */
 int wv_argmax_dev(const float* d_logits, int n, int* d_index, void* stream);
 int wv_argmax(const float* d_logits, int n, int* index_host, void* stream);
+/* Top-K sampling with temperature on the device — sampling.SampleTopK (model/sampling/topk.go:11-50): greedy when
+ * top_k == 1, temperature <= 0 or `deterministic`; otherwise the top_k largest of logit / temperature (every logit when
+ * top_k <= 0 or top_k >= n; at most 1024 candidates, else WV_EARG), softmax weights in float64, and the draw
+ * r = u01 * sum walks them from the largest down. The reference draws u01 from math/rand's global source inside the
+ * call; here the caller passes it (0 <= u01 <= 1). Equal values, whose order the reference's unstable sort leaves open,
+ * go by rising index. */
+int wv_topk_sample_dev(const float* d_logits, int n, int top_k, float temperature, int deterministic, double u01,
+                       int* d_index, void* stream);
+int wv_topk_sample(const float* d_logits, int n, int top_k, float temperature, int deterministic, double u01,
+                   int* index_host, void* stream);
 
 /* Dequantise the resident blob to f32 on the device and copy rows*cols floats out —
  * quant.Unpack (quant/unpack.go:4-34); results are bit-identical to it. */
 int wv_unpack(uint64_t key, float* out_host);
 int wv_unpack_dev(uint64_t key, float* d_out, void* stream);
+/* One output row as f32 — quant.DecodeRow (quant/decode_row.go:7-38): the Cols values Unpack gives for `row`
+ * (counted within the rows this device holds); WV_ESHAPE when row is out of range or ndst < Cols, as the reference's
+ * shape error. The reference refuses FormatNone here (its weights.DecodeRow covers it); this entry takes it too. */
+int wv_decode_row(uint64_t key, int row, float* dst_host, int ndst);
+int wv_decode_row_dev(uint64_t key, int row, float* d_dst, void* stream);
 
 /* quant.Pack on the device (quant/pack.go:4-31; dense.Layer.Pack, layers/dense/dense.go:84-89):
  * packs rows x cols f32 weights (host pointer) into caller-allocated Raw / Scales / Mins of

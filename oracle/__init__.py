@@ -220,6 +220,26 @@ def argmax(logits: np.ndarray) -> int:
     return int(lib().wvo_argmax(v.ctypes.data_as(C.c_void_p), C.c_int64(v.size)))
 
 
+def topk_sample(logits: np.ndarray, top_k: int, temperature: float, deterministic: bool, u: float) -> int:
+    """sampling.SampleTopK (model/sampling/topk.go:11-50); u stands for the reference's rand.Float64()."""
+    v = np.ascontiguousarray(logits, np.float32).reshape(-1)
+    f = lib().wvo_topk_sample
+    f.argtypes = [C.c_void_p, C.c_int64, C.c_int, C.c_float, C.c_int, C.c_double]
+    return int(f(v.ctypes.data_as(C.c_void_p), v.size, int(top_k), float(temperature), 1 if deterministic else 0, float(u)))
+
+
+def decode_row(b: Blob, row: int) -> np.ndarray:
+    """quant.DecodeRow (quant/decode_row.go:7-38)."""
+    out = np.zeros(b.cols, np.float32)
+    cb = b._c()
+    f = lib().wvo_decode_row
+    f.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int64]
+    rc = f(C.byref(cb), int(row), out.ctypes.data_as(C.c_void_p), out.size)
+    if rc:
+        raise ValueError(f"wvo_decode_row -> {rc}")
+    return out
+
+
 # core.ActivationType (core/layer.go:91-98)
 ACTIVATIONS = {"Linear": -1, "ReLU": 0, "SiLU": 1, "GELU": 2, "Tanh": 3, "Sigmoid": 4, "LeakyReLU": 5, "ReLU2": 6}
 

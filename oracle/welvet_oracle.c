@@ -1386,3 +1386,124 @@ void wvo_silu_mul(const float *gate, const float *up, float *out, int n) {
     out[i] = (float)(g / (1 + exp(-g)) * (double)up[i]);
   }
 }
+
+/* ---------- quant.DecodeRow (quant/decode_row.go:7-187, binary_g128.go:130-157, affine_g64.go:121-175) ----------
+ * One output row of a packed blob. Q8_0, Q4_0, ternary and binary walk the flat index themselves; the row-aligned
+ * layouts walk their words; everything else copies the row out of a full Unpack. FormatNone is refused (-2), a row
+ * out of range or a short dst is a shape error (-1). */
+int wvo_decode_row(const wvo_blob *b, int row, float *dst, int64_t ndst) {
+  if (!b) return -2;
+  if (row < 0 || row >= b->rows || ndst < b->cols) return -1;
+  const int cols = b->cols;
+  const int64_t base = (int64_t)row * cols, n = (int64_t)b->rows * cols;
+  switch (b->format) {
+  case F_NONE: return -2;
+  case F_Q8_0:
+    for (int c = 0; c < cols; c++) {
+      int64_t i = base + c, bi = i / 32, j = i % 32, off = bi * 36;
+      if ((uint64_t)(off + 4 + j) >= b->nraw || i >= n) { dst[c] = 0; continue; }
+      dst[c] = (float)(int8_t)b->raw[off + 4 + j] * get_f32(b->raw + off);
+    }
+    return 0;
+  case F_Q4_0:
+    for (int c = 0; c < cols; c++) {
+      int64_t i = base + c;
+      if (i >= n) { dst[c] = 0; continue; }
+      int64_t bi = i / 32, j = i % 32, off = bi * 20;
+      if ((uint64_t)(off + 4 + j / 2) >= b->nraw) { dst[c] = 0; continue; }
+      uint8_t w = b->raw[off + 4 + j / 2];
+      int8_t q = (int8_t)((j % 2 == 0) ? (w & 0xF) : (w >> 4));
+      if (q > 7) q -= 16;
+      dst[c] = (float)q * get_f32(b->raw + off);
+    }
+    return 0;
+  case F_TERNARY:
+    for (int c = 0; c < cols; c++) {
+      int64_t i = base + c;
+      if (i >= n) { dst[c] = 0; continue; }
+      int64_t g = i / 16, j = i % 16;
+      if ((uint64_t)(g * 4 + 4) > b->nraw) { dst[c] = 0; continue; }
+      uint32_t code = (get_u32(b->raw + g * 4) >> (j * 2)) & 3;
+      float scale = (uint64_t)g < b->ns ? b->scales[g] : 1.0f;
+      dst[c] = code == 0 ? -scale : (code == 2 ? scale : 0.0f);
+    }
+    return 0;
+  case F_BINARY:
+    if (binary_is_g128(b)) {
+      int gpr = cols / 128, wpr = cols / 32;
+      for (int g = 0; g < gpr; g++) {
+        int64_t si = (int64_t)row * gpr + g;
+        float scale = (uint64_t)si < b->ns ? b->scales[si] : 1.0f;
+        for (int wi = 0; wi < 4; wi++) {
+          uint32_t word = get_u32(b->raw + ((int64_t)row * wpr + g * 4 + wi) * 4);
+          for (int j = 0; j < 32; j++) dst[g * 128 + wi * 32 + j] = ((word >> j) & 1) ? scale : -scale;
+        }
+      }
+      return 0;
+    }
+    for (int c = 0; c < cols; c++) {
+      int64_t i = base + c;
+      if (i >= n) { dst[c] = 0; continue; }
+      int64_t g = i / 32, j = i % 32;
+      if ((uint64_t)(g * 4 + 4) > b->nraw) { dst[c] = 0; continue; }
+      float scale = (uint64_t)g < b->ns ? b->scales[g] : 1.0f;
+      dst[c] = ((get_u32(b->raw + g * 4) >> j) & 1) ? scale : -scale;
+    }
+    return 0;
+  case F_AFFINE: {
+    int group = b->block_weights > 0 ? b->block_weights : 64;
+    int wpr = cols / 8, gpr = cols / group, wig = group / 8;
+    for (int g = 0; g < gpr; g++) {
+      int64_t si = (int64_t)row * gpr + g;
+      float s = (uint64_t)si < b->ns ? b->scales[si] : 1.0f;
+      float beta = (uint64_t)si < b->nm ? b->mins[si] : 0.0f;
+      for (int wi = 0; wi < wig; wi++) {
+        uint32_t word = get_u32(b->raw + ((int64_t)row * wpr + g * wig + wi) * 4);
+        for (int j = 0; j < 8; j++) dst[g * group + wi * 8 + j] = s * (float)((word >> (j * 4)) & 15) + beta;
+      }
+    }
+    return 0;
+  }
+  default: {
+    float *all = (float *)malloc((size_t)n * sizeof(float));
+    if (!all) return -4;
+    int rc = wvo_unpack(b, all);
+    if (!rc) memcpy(dst, all + base, (size_t)cols * sizeof(float));
+    free(all);
+    return rc;
+  }
+  }
+}
+
+/* ---------- top-K sampling (model/sampling/topk.go:11-50) ----------
+ * Greedy when top_k == 1, temperature <= 0 or deterministic. Otherwise candidates are logit / temperature (float32),
+ * sorted by value descending, cut to top_k when 0 < top_k < n; p_i = exp(float64(val_i - max)) with the subtraction
+ * in float32; r = u * sum, and the first i with r <= running sum wins, else the last candidate. `u` stands for the
+ * reference's rand.Float64(). sort.Slice is not stable, so the order of equal values is open in the reference; this
+ * restatement orders them by rising index. */
+typedef struct { int32_t idx; float val; } topk_pair;
+static int topk_cmp(const void *a, const void *b) {
+  const topk_pair *p = (const topk_pair *)a, *q = (const topk_pair *)b;
+  if (p->val > q->val) return -1;
+  if (p->val < q->val) return 1;
+  return p->idx < q->idx ? -1 : (p->idx > q->idx ? 1 : 0);
+}
+int wvo_topk_sample(const float *logits, int64_t n, int top_k, float temperature, int deterministic, double u) {
+  if (n <= 0) return 0;
+  if (top_k == 1 || temperature <= 0 || deterministic) return wvo_argmax(logits, n);
+  topk_pair *cands = (topk_pair *)malloc((size_t)n * sizeof(topk_pair));
+  if (!cands) return -1;
+  for (int64_t i = 0; i < n; i++) { cands[i].idx = (int32_t)i; cands[i].val = logits[i] / temperature; }
+  qsort(cands, (size_t)n, sizeof(topk_pair), topk_cmp);
+  int64_t k = (top_k > 0 && top_k < n) ? top_k : n;
+  float maxv = cands[0].val;
+  double *probs = (double *)malloc((size_t)k * sizeof(double));
+  if (!probs) { free(cands); return -1; }
+  double sum = 0;
+  for (int64_t i = 0; i < k; i++) { float d = cands[i].val - maxv; probs[i] = exp((double)d); sum += probs[i]; }
+  double r = u * sum, acc = 0.0;
+  int pick = cands[k - 1].idx;
+  for (int64_t i = 0; i < k; i++) { acc += probs[i]; if (r <= acc) { pick = cands[i].idx; break; } }
+  free(probs); free(cands);
+  return pick;
+}

@@ -9,6 +9,13 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 
+# The tests load the library variant with the development hooks (kernel-choice steering) when it has been built;
+# the product library otherwise, and the tests that steer kernels skip.
+_DEV_LIB = os.path.join(ROOT, "welvet_b200", "libwelvet_cuda_dev.so")
+if "WELVET_CUDA_LIB" not in os.environ and os.path.exists(_DEV_LIB):
+    os.environ["WELVET_CUDA_LIB"] = _DEV_LIB
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (sm_100)")
 
@@ -50,6 +57,14 @@ def wv():
     import welvet_b200
     welvet_b200.init(0)
     return welvet_b200
+
+
+@pytest.fixture
+def hooks(wv):
+    """The development hooks of the loaded library; skips where it was built without them."""
+    if not wv._lib.has_dev_hooks():
+        pytest.skip("library built without -DWV_DEV_HOOKS")
+    return wv._lib.lib()
 
 
 def to_product_blob(wvpkg, ob):

@@ -30,6 +30,23 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(L, s), s
 
 
+def test_product_library_has_no_development_hooks():
+    """The product library exports the declared ABI and none of the tuning hooks; the variant the tests load
+    (built with -DWV_DEV_HOOKS) exports both."""
+    m = _lib()
+    here = os.path.join(ROOT, "welvet_b200")
+    prod = C.CDLL(os.path.join(here, "libwelvet_cuda.so"))
+    for s in m.SYMBOLS:
+        assert hasattr(prod, s), s
+    for s in m.DEV_HOOKS:
+        assert not hasattr(prod, s), s
+    dev_path = os.path.join(here, "libwelvet_cuda_dev.so")
+    if os.path.exists(dev_path):
+        dev = C.CDLL(dev_path)
+        for s in m.SYMBOLS + m.DEV_HOOKS:
+            assert hasattr(dev, s), s
+
+
 def test_status_codes_without_a_device():
     m = _lib()
     L = m.lib()

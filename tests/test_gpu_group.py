@@ -27,7 +27,7 @@ def _stores(wv, f, shapes, cols, seed):
 @pytest.mark.parametrize("fmt", ["Q4_K", "Q8_0", "Q4_0", "IQ3_S"])
 @pytest.mark.parametrize("shapes", [(4096, 1024, 1024), (1500, 1500), (96, 40, 8, 300)], ids=["qkv", "gate_up", "four_ragged_rows"])
 @pytest.mark.parametrize("batch", [1, 3])
-def test_group_equals_separate_launches(wv, fmt, shapes, batch):
+def test_group_equals_separate_launches(wv, hooks, fmt, shapes, batch):
     cols = 4096
     L = wv._lib.lib()
     obs, sts = _stores(wv, fmt, shapes, cols, 40)

@@ -16,10 +16,10 @@ SHAPES = [(100, 4096), (4096, 4096), (333, 14336), (48, 11264), (17, 1024)]
 
 
 @pytest.fixture
-def mma(wv):
-    wv._lib.lib().wv_set_tma_tuning(24, 0)
+def mma(wv, hooks):
+    hooks.wv_set_tma_tuning(24, 0)
     yield wv
-    wv._lib.lib().wv_set_tma_tuning(0, 0)
+    hooks.wv_set_tma_tuning(0, 0)
 
 
 def _check(wv, f, bw, rows, cols, x, w=None):

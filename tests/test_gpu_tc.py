@@ -18,11 +18,11 @@ SHAPES = [(100, 4096), (333, 14336), (48, 11264), (17, 1024), (2500, 2048)]
 
 
 @pytest.fixture
-def tc(wv):
-    wv._lib.lib().wv_set_tma_tuning(30, 0)
+def tc(wv, hooks):
+    hooks.wv_set_tma_tuning(30, 0)
     yield wv
-    wv._lib.lib().wv_set_tma_tuning(0, 0)
-    wv._lib.lib().wv_set_act_width(0)
+    hooks.wv_set_tma_tuning(0, 0)
+    hooks.wv_set_act_width(0)
 
 
 def _run(wv, f, bw, rows, cols, x, w=None):

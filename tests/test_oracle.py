@@ -213,3 +213,39 @@ def test_oracle_against_reference_dump():
         if has_simd:
             np.testing.assert_allclose(O.matvec_simd(ob, x, 1), y_simd, rtol=1e-6, atol=1e-7, err_msg=tag + ": SIMD path")
     assert off == len(data)
+
+
+def test_topk_restatement_known_answers():
+    """sampling.SampleTopK by hand: logits (0, ln 2, ln 4, -9) at temperature 1, top 3 -> weights 1, 1/2, 1/4 in the
+    order index 2, 1, 0 (sum 1.75); the draw u * 1.75 falls in [0, 1] -> 2, (1, 1.5] -> 1, (1.5, 1.75] -> 0."""
+    v = np.array([0.0, np.log(2.0), np.log(4.0), -9.0], np.float32)
+    assert O.topk_sample(v, 3, 1.0, False, 0.0) == 2
+    assert O.topk_sample(v, 3, 1.0, False, 1.0 / 1.75 - 1e-9) == 2
+    assert O.topk_sample(v, 3, 1.0, False, 1.0 / 1.75 + 1e-6) == 1
+    assert O.topk_sample(v, 3, 1.0, False, 1.5 / 1.75 + 1e-6) == 0
+    assert O.topk_sample(v, 3, 1.0, False, 1.0) == 0
+    assert O.topk_sample(v, 0, 1.0, False, 1.0) == 3          # top_k <= 0: every logit is a candidate
+    assert O.topk_sample(v, 9, 1.0, False, 1.0) == 3          # top_k >= n as well
+    for args in ((1, 1.0, False), (3, 0.0, False), (3, -1.0, False), (3, 1.0, True)):   # the greedy short-cuts
+        assert O.topk_sample(v, *args, 0.9) == 2
+    assert O.topk_sample(np.zeros(0, np.float32), 3, 1.0, False, 0.5) == 0
+    t = np.array([1, 5, 5, 5, 2], np.float32)                 # equal values go by rising index here
+    assert [O.topk_sample(t, 2, 1.0, False, u) for u in (0.1, 0.9)] == [1, 2]
+    # temperature divides in float32 before the ordering: a high temperature flattens the weights
+    hot = [O.topk_sample(v, 3, 100.0, False, u) for u in (0.2, 0.5, 0.9)]
+    assert hot == [2, 1, 0]
+
+
+@pytest.mark.parametrize("case", CASES, ids=case_id)
+def test_decode_row_restatement_equals_unpack_rows(case):
+    f, bw, dt = case
+    if f == "none":
+        pytest.skip("quant.DecodeRow refuses FormatNone")
+    rows, cols = (9, 256) if (f == "AffinePacked" or bw == 128) else (9, 200)
+    w = np.random.default_rng(11).normal(0, 0.02, rows * cols).astype(np.float32)
+    ob = O.pack(f, w, rows, cols, bw, dt)
+    full = O.unpack(ob).reshape(rows, cols)
+    for r in range(rows):
+        assert O.decode_row(ob, r).tobytes() == full[r].tobytes()
+    with pytest.raises(ValueError):
+        O.decode_row(ob, rows)

@@ -4,7 +4,7 @@ Host-side mirror of the reference's quant / weights / layers/dense call surface 
 of libwelvet_cuda.so. The library must be built (`python -m welvet_b200.build`); there is no
 CPU fallback.
 """
-from . import _lib, decode, dense, quant, sampling, weights  # noqa: F401
+from . import _lib, decode, dense, entity, quant, sampling, weights  # noqa: F401
 from ._lib import WelvetError, init  # noqa: F401
 
-__all__ = ["quant", "weights", "dense", "decode", "init", "WelvetError"]
+__all__ = ["quant", "weights", "dense", "decode", "entity", "sampling", "init", "WelvetError"]

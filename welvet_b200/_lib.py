@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.environ.get("WELVET_CUDA_LIB") or os.path.join(_HERE, "libwelvet_cuda.so")   # the variable selects a development build
+# WELVET_CUDA_LIB selects another build of the library (the test-suite loads the variant with the development hooks)
+LIB_PATH = os.environ.get("WELVET_CUDA_LIB") or os.path.join(_HERE, "libwelvet_cuda.so")
 
 # Every symbol include/welvet_cuda.h declares.
 SYMBOLS = [
@@ -21,9 +22,11 @@ SYMBOLS = [
     "wv_argmax_dev", "wv_argmax", "wv_matvec_dev_multi", "wv_matvec_dev_gather", "wv_gather_alloc", "wv_gather_open", "wv_gather_close", "wv_gather_free", "wv_gather_read", "wv_gather_signal", "wv_gather_wait",
     "wv_matvec_dev_swiglu", "wv_matvec_dev_add", "wv_matvec_dev_group_gather", "wv_rmsnorm_dev", "wv_rope_cache_dev",
     "wv_attn_decode_dev", "wv_silu_mul_dev", "wv_residual_add_dev",
+    "wv_topk_sample_dev", "wv_topk_sample", "wv_decode_row", "wv_decode_row_dev",
 ]
 
-# Development hooks (csrc/wv_dev_hooks.h): exported for tests and tuning runs, not part of the public header.
+# Development hooks (csrc/wv_dev_hooks.h): only in a library built with -DWV_DEV_HOOKS (libwelvet_cuda_dev.so),
+# for tests and tuning runs; the product library does not export them.
 DEV_HOOKS = ["wv_set_tuning", "wv_set_tma_tuning", "wv_set_act_width"]
 
 WV_OK, WV_ESHAPE, WV_EFORMAT, WV_ENOMEM, WV_ECUDA, WV_ETIMEOUT, WV_ENOTFOUND, WV_EINIT, WV_EARG = (
@@ -57,12 +60,13 @@ def lib() -> C.CDLL:
         L.wv_cache_clear.restype = None
         L.wv_cache_set_limit.restype = None
         L.wv_cache_set_limit.argtypes = [u64]
-        L.wv_set_tuning.restype = None
-        L.wv_set_tuning.argtypes = [i, i, i, i]
-        L.wv_set_tma_tuning.restype = None
-        L.wv_set_tma_tuning.argtypes = [i, i]
-        L.wv_set_act_width.restype = None
-        L.wv_set_act_width.argtypes = [i]
+        if hasattr(L, "wv_set_tuning"):
+            L.wv_set_tuning.restype = None
+            L.wv_set_tuning.argtypes = [i, i, i, i]
+            L.wv_set_tma_tuning.restype = None
+            L.wv_set_tma_tuning.argtypes = [i, i]
+            L.wv_set_act_width.restype = None
+            L.wv_set_act_width.argtypes = [i]
         L.wv_init.argtypes = [i]
         L.wv_blob_upload.argtypes = [u64, i, i, i, i, i, vp, sz, vp, sz, vp, sz]
         L.wv_blob_upload_wire.argtypes = [u64, i, i, i, i, vp, sz]
@@ -93,6 +97,10 @@ def lib() -> C.CDLL:
         L.wv_attn_decode_dev.argtypes = [vp, vp, vp, vp, i, i, i, i, i, C.c_float, vp]
         L.wv_silu_mul_dev.argtypes = [vp, vp, vp, i, vp]
         L.wv_residual_add_dev.argtypes = [vp, vp, i, vp]
+        L.wv_topk_sample_dev.argtypes = [vp, i, i, C.c_float, i, C.c_double, vp, vp]
+        L.wv_topk_sample.argtypes = [vp, i, i, C.c_float, i, C.c_double, C.POINTER(i), vp]
+        L.wv_decode_row.argtypes = [u64, i, vp, i]
+        L.wv_decode_row_dev.argtypes = [u64, i, vp, vp]
         L.wv_unpack.argtypes = [u64, vp]
         L.wv_unpack_dev.argtypes = [u64, vp, vp]
         L.wv_pack_sizes.argtypes = [i, i, i, i, i, C.POINTER(sz), C.POINTER(sz), C.POINTER(sz)]
@@ -100,6 +108,10 @@ def lib() -> C.CDLL:
         L.wv_pack_upload_dev.argtypes = [u64, i, i, i, vp, i, i, vp]
         _lib = L
     return _lib
+
+
+def has_dev_hooks() -> bool:
+    return hasattr(lib(), "wv_set_tuning")
 
 
 def check(rc: int) -> None:

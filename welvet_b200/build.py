@@ -1,6 +1,6 @@
 """In-tree build of libwelvet_cuda.so for sm_100a (nvcc cross-compiles without a GPU).
 
-    python -m welvet_b200.build [--force] [--verbose]
+    python -m welvet_b200.build [--all] [--force] [--verbose]
 
 wv_layout.cu and wv_pack.cu hold the bit-exact arithmetic (unpack / pack) and are compiled
 with --fmad=false so that no multiply-add is contracted; the GEMV may use FMA.
@@ -14,14 +14,21 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-OBJ = os.path.join(HERE, "build" + os.environ.get("WV_LIB_SUFFIX", ""))
-# WV_LIB_SUFFIX builds a second library beside the product one (development variants, e.g. with -DWV_PHASES)
-_SUFFIX = os.environ.get("WV_LIB_SUFFIX", "")
-LIB = os.path.join(HERE, f"libwelvet_cuda{_SUFFIX}.so")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
+# Variants beside the product library: "" is libwelvet_cuda.so (what the package loads); "_dev" adds the development
+# hooks of csrc/wv_dev_hooks.h (-DWV_DEV_HOOKS), which the test-suite uses to steer kernel choices. WV_LIB_SUFFIX /
+# WV_NVCC_EXTRA build any other variant from the command line.
+VARIANTS = {"": [], "_dev": ["-DWV_DEV_HOOKS"]}
+
+
+def lib_path(suffix: str = "") -> str:
+    return os.path.join(HERE, f"libwelvet_cuda{suffix}.so")
+
+
+LIB = lib_path(os.environ.get("WV_LIB_SUFFIX", ""))
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
-COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-I", INCLUDE] + os.environ.get("WV_NVCC_EXTRA", "").split()
+COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-I", INCLUDE]
 SOURCES = {
     "wv_layout.cu": ["--fmad=false"],
     "wv_pack.cu": ["--fmad=false"],
@@ -39,8 +46,8 @@ def _newest_dep() -> float:
     return max(os.path.getmtime(d) for d in deps)
 
 
-def _compile(src: str, extra: list[str], verbose: bool) -> str:
-    obj = os.path.join(OBJ, src.replace(".cu", ".o"))
+def _compile(src: str, extra: list[str], objdir: str, verbose: bool) -> str:
+    obj = os.path.join(objdir, src.replace(".cu", ".o"))
     cmd = ["nvcc", *ARCH, *COMMON, *extra, "-c", os.path.join(CSRC, src), "-o", obj]
     if verbose:
         cmd.insert(1, "-Xptxas")
@@ -53,19 +60,32 @@ def _compile(src: str, extra: list[str], verbose: bool) -> str:
     return obj
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile every CUDA source for sm_100a and link the shared library."""
-    if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= _newest_dep():
-        return LIB
-    os.makedirs(OBJ, exist_ok=True)
+def build(force: bool = False, verbose: bool = False, suffix: str | None = None) -> str:
+    """Compile every CUDA source for sm_100a and link one variant of the shared library."""
+    if suffix is None:
+        suffix = os.environ.get("WV_LIB_SUFFIX", "")
+    out = lib_path(suffix)
+    if not force and os.path.exists(out) and os.path.getmtime(out) >= _newest_dep():
+        return out
+    flags = VARIANTS.get(suffix, []) + os.environ.get("WV_NVCC_EXTRA", "").split()
+    objdir = os.path.join(HERE, "build" + suffix)
+    os.makedirs(objdir, exist_ok=True)
     with ThreadPoolExecutor(max_workers=8) as ex:
-        objs = list(ex.map(lambda kv: _compile(kv[0], kv[1], verbose), SOURCES.items()))
-    cmd = ["nvcc", *ARCH, "-shared", "-cudart", "static", "-o", LIB, *objs]
+        objs = list(ex.map(lambda kv: _compile(kv[0], kv[1] + flags, objdir, verbose), SOURCES.items()))
+    cmd = ["nvcc", *ARCH, "-shared", "-cudart", "static", "-o", out, *objs]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stderr}")
-    return LIB
+    return out
+
+
+def build_all(force: bool = False) -> list[str]:
+    """The product library and the development variant the tests load."""
+    return [build(force, suffix=s) for s in VARIANTS]
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    if "--all" in sys.argv:
+        print("\n".join(build_all(force="--force" in sys.argv)))
+    else:
+        print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -442,6 +442,46 @@ extern "C" int wv_argmax(const float* d_logits, int n, int* index_host, void* st
   return WV_OK;
 }
 
+int wv_launch_topk_sample(const float* d_logits, int n, int k, float temperature, double u01, int* d_out, cudaStream_t st);   // wv_decode.cu
+
+// sampling.SampleTopK (model/sampling/topk.go:11-50). Greedy (top_k == 1, temperature <= 0 or `deterministic`)
+// is ArgMax; otherwise K = top_k, or every logit when top_k <= 0 or top_k >= n, and K must not exceed 1024.
+static int topk_launch(const char* who, const float* d_logits, int n, int top_k, float temperature, int deterministic, double u01,
+                       int* d_index, cudaStream_t st) {
+  if (n <= 0 || top_k == 1 || !(temperature > 0.0f) || deterministic) return wv_launch_argmax(d_logits, n, d_index, st);
+  if (!(u01 >= 0.0 && u01 <= 1.0)) { wv_set_error("%s: the uniform draw must lie in [0, 1]", who); return WV_EARG; }
+  const int k = (top_k > 0 && top_k < n) ? top_k : n;
+  if (k > 1024) { wv_set_error("%s: %d candidates (top_k = %d over %d logits); the device sampler takes at most 1024", who, k, top_k, n); return WV_EARG; }
+  return wv_launch_topk_sample(d_logits, n, k, temperature, u01, d_index, st);
+}
+extern "C" int wv_topk_sample_dev(const float* d_logits, int n, int top_k, float temperature, int deterministic, double u01,
+                                  int* d_index, void* stream) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!d_logits || !d_index || n < 0) { wv_set_error("wv_topk_sample_dev: bad argument"); return WV_EARG; }
+  return topk_launch("wv_topk_sample_dev", d_logits, n, top_k, temperature, deterministic, u01, d_index, static_cast<cudaStream_t>(stream));
+}
+extern "C" int wv_topk_sample(const float* d_logits, int n, int top_k, float temperature, int deterministic, double u01,
+                              int* index_host, void* stream) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!d_logits || !index_host || n < 0) { wv_set_error("wv_topk_sample: bad argument"); return WV_EARG; }
+  static int* h_idx = nullptr;     // mapped pinned word, as in wv_argmax
+  static int* d_idx = nullptr;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lk(mu);
+  if (!h_idx) {
+    if (cudaHostAlloc(&h_idx, sizeof(int), cudaHostAllocMapped) != cudaSuccess || cudaHostGetDevicePointer(&d_idx, h_idx, 0) != cudaSuccess) {
+      cudaGetLastError(); h_idx = nullptr; wv_set_error("wv_topk_sample: no pinned word"); return WV_ENOMEM;
+    }
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if ((rc = topk_launch("wv_topk_sample", d_logits, n, top_k, temperature, deterministic, u01, d_idx, st))) return rc;
+  CUDA_TRY(cudaStreamSynchronize(st));
+  *index_host = *h_idx;
+  return WV_OK;
+}
+
 extern "C" int wv_matvec_dev_multi(const uint64_t* keys, int n, const float* dx, float* const* dy, int batch, int in, const int* out,
                                    void* stream) {
   int rc = ensure_init();
@@ -771,6 +811,35 @@ extern "C" int wv_unpack(uint64_t key, float* out_host) {
   cudaError_t c3 = cudaStreamSynchronize(g_stream);
   cudaFree(d);
   if (rc || c2 != cudaSuccess || c3 != cudaSuccess) { wv_set_error("wv_unpack failed: %s", cudaGetErrorString(c3 != cudaSuccess ? c3 : c2)); return rc ? rc : WV_ECUDA; }
+  return WV_OK;
+}
+
+// quant.DecodeRow (quant/decode_row.go:7-38): row `row` of the rows this device holds, Cols floats.
+extern "C" int wv_decode_row_dev(uint64_t key, int row, float* d_dst, void* stream) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!d_dst) { wv_set_error("wv_decode_row_dev: null pointer"); return WV_EARG; }
+  Entry e;
+  if ((rc = lookup(key, &e))) return rc;
+  if (row < 0 || row >= e.blob.rows) { wv_set_error("wv_decode_row_dev: shape row=%d rows=%d cols=%d", row, e.blob.rows, e.blob.cols); return WV_ESHAPE; }
+  return wv_launch_unpack_rows(e.blob, row, 1, d_dst, static_cast<cudaStream_t>(stream));
+}
+extern "C" int wv_decode_row(uint64_t key, int row, float* dst_host, int ndst) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!dst_host) { wv_set_error("wv_decode_row: null pointer"); return WV_EARG; }
+  Entry e;
+  if ((rc = lookup(key, &e))) return rc;
+  if (row < 0 || row >= e.blob.rows || ndst < e.blob.cols) {
+    wv_set_error("wv_decode_row: shape row=%d cols=%d dst=%d", row, e.blob.cols, ndst); return WV_ESHAPE;
+  }
+  float* d = nullptr;
+  if (cudaMalloc(&d, (size_t)e.blob.cols * 4) != cudaSuccess) { cudaGetLastError(); wv_set_error("wv_decode_row: cudaMalloc failed"); return WV_ENOMEM; }
+  rc = wv_launch_unpack_rows(e.blob, row, 1, d, g_stream);
+  cudaError_t c2 = cudaMemcpyAsync(dst_host, d, (size_t)e.blob.cols * 4, cudaMemcpyDeviceToHost, g_stream);
+  cudaError_t c3 = cudaStreamSynchronize(g_stream);
+  cudaFree(d);
+  if (rc || c2 != cudaSuccess || c3 != cudaSuccess) { wv_set_error("wv_decode_row failed: %s", cudaGetErrorString(c3 != cudaSuccess ? c3 : c2)); return rc ? rc : WV_ECUDA; }
   return WV_OK;
 }
 

@@ -135,6 +135,7 @@ void wv_set_error(const char* fmt, ...);
 // Launchers implemented across the .cu files.
 int wv_launch_relayout(const WvDevBlob& dst, const uint8_t* d_raw, size_t nraw, cudaStream_t st);
 int wv_launch_unpack(const WvDevBlob& b, float* d_out, cudaStream_t st);
+int wv_launch_unpack_rows(const WvDevBlob& b, int row, int nrows, float* d_out, cudaStream_t st);
 int wv_launch_gemv(const WvDevBlob& b, const float* dx, float* dy, int batch, int row_begin, int row_end,
                    cudaStream_t st);
 int wv_launch_pack(int format, int dtype, int group, const float* d_w, int rows, int cols, uint8_t* d_raw,

@@ -275,3 +275,105 @@ int wv_launch_silu_mul(const float* dgate, const float* dup, float* dout, int n,
 int wv_launch_residual_add(float* ddst, const float* dadd, int n, cudaStream_t st) {
   return launch_small(residual_add_kernel, n, st, ddst, dadd, n);
 }
+
+// ------------------------------------------------------------------ top-K sampling over the logits
+// sampling.SampleTopK (model/sampling/topk.go:11-50) for 1 <= K <= 1024 without reading the logits back:
+// candidates are v / temperature (a float32 divide), ordered by value descending; p_i = exp(float64(val_i - max))
+// with the subtraction in float32; the draw r = u * sum(p) walks the running sum in that order and the first
+// candidate with r <= acc wins, the last one otherwise. The reference takes u from math/rand's global source; here
+// the caller passes it, so that the host keeps the one random stream. sort.Slice leaves the order of equal values
+// open; here equal values go by rising index. A NaN logit is ordered by its bit pattern (the reference's order with
+// NaN is whatever its sort happens to do).
+//
+// One CTA. Each logit becomes a 64-bit word (ordered value bits : ~index), all distinct; a most-significant-digit
+// radix select (8 bits a pass, stopping as soon as a bucket holds exactly what is still needed) finds the K-th
+// largest word, the K words at or above it are gathered and sorted by a bitonic network in shared memory, and
+// thread 0 does the two short sequential float64 walks so that the sums round as the reference's do.
+#define TOPK_MAX 1024
+__device__ __forceinline__ unsigned long long topk_word(float v, float temperature, int i) {
+  const float val = __fdiv_rn(v, temperature);
+  unsigned u = __float_as_uint(val);
+  u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+  return ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned)i);
+}
+__global__ void __launch_bounds__(1024, 1) topk_sample_kernel(const float* __restrict__ v, int n, int k, float temperature, double u01,
+                                                              int* __restrict__ out) {
+  __shared__ unsigned s_hist[256];
+  __shared__ unsigned long long s_cand[TOPK_MAX];
+  __shared__ double s_p[TOPK_MAX];
+  __shared__ unsigned long long s_prefix;
+  __shared__ unsigned s_need, s_done, s_count;
+  const int tid = threadIdx.x;
+  if (tid == 0) { s_prefix = 0ull; s_need = (unsigned)k; s_done = 0u; s_count = 0u; }
+  __syncthreads();
+  unsigned long long thresh = 0ull;
+  for (int pass = 0; pass < 8; pass++) {
+    const int shift = 56 - 8 * pass;
+    if (tid < 256) s_hist[tid] = 0u;
+    __syncthreads();
+    const unsigned long long prefix = s_prefix;
+    const unsigned long long himask = pass == 0 ? 0ull : (~0ull << (shift + 8));
+    for (int i = tid; i < n; i += 1024) {
+      const unsigned long long w = topk_word(v[i], temperature, i);
+      if ((w & himask) == prefix) atomicAdd(&s_hist[(unsigned)(w >> shift) & 255u], 1u);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      unsigned need = s_need, d = 255u;
+      for (;; d--) {               // from the top digit down: the bucket where the running count reaches `need`
+        const unsigned c = s_hist[d];
+        if (c >= need || d == 0u) { if (c == need) s_done = 1u; break; }
+        need -= c;
+      }
+      s_need = need;
+      s_prefix = prefix | ((unsigned long long)d << shift);
+    }
+    __syncthreads();
+    thresh = s_prefix;             // low digits still zero: every word of the chosen bucket is >= thresh
+    if (s_done) break;
+  }
+  for (int i = tid; i < n; i += 1024) {
+    const unsigned long long w = topk_word(v[i], temperature, i);
+    if (w >= thresh) { const unsigned slot = atomicAdd(&s_count, 1u); if (slot < TOPK_MAX) s_cand[slot] = w; }
+  }
+  __syncthreads();
+  const int cnt = min((int)s_count, TOPK_MAX);   // == k by construction
+  int p2 = 1;
+  while (p2 < cnt) p2 <<= 1;
+  for (int i = tid; i < p2; i += 1024) if (i >= cnt) s_cand[i] = 0ull;
+  __syncthreads();
+  for (int size = 2; size <= p2; size <<= 1) {   // bitonic sort, descending
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int i = tid; i < p2; i += 1024) {
+        const int j = i ^ stride;
+        if (j > i) {
+          const unsigned long long a = s_cand[i], b = s_cand[j];
+          const bool desc = (i & size) == 0;
+          if (desc ? (a < b) : (a > b)) { s_cand[i] = b; s_cand[j] = a; }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  auto value_of = [](unsigned long long w) {
+    unsigned u = (unsigned)(w >> 32);
+    u = (u & 0x80000000u) ? (u & 0x7FFFFFFFu) : ~u;
+    return __uint_as_float(u);
+  };
+  const float maxv = value_of(s_cand[0]);
+  for (int i = tid; i < cnt; i += 1024) s_p[i] = exp((double)__fsub_rn(value_of(s_cand[i]), maxv));
+  __syncthreads();
+  if (tid == 0) {
+    double sum = 0.0;
+    for (int i = 0; i < cnt; i++) sum += s_p[i];
+    const double r = u01 * sum;
+    double acc = 0.0;
+    int pick = cnt - 1;
+    for (int i = 0; i < cnt; i++) { acc += s_p[i]; if (r <= acc) { pick = i; break; } }
+    *out = (int)(0xFFFFFFFFu - (unsigned)(s_cand[pick] & 0xFFFFFFFFull));
+  }
+}
+int wv_launch_topk_sample(const float* d_logits, int n, int k, float temperature, double u01, int* d_out, cudaStream_t st) {
+  topk_sample_kernel<<<1, 1024, 0, st>>>(d_logits, n, k, temperature, u01, d_out);
+  return cudaGetLastError() == cudaSuccess ? WV_OK : WV_ECUDA;
+}

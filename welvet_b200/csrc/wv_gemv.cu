@@ -409,7 +409,9 @@ int wv_sm_count() {
 // Tuning knobs (rows per warp, column split, prefetch depth) can be overridden for
 // experiments through wv_set_tuning(); 0 keeps the built-in choice.
 static int g_tune_r = 0, g_tune_s = 0, g_tune_d = 0, g_tune_grid = 0;
+#ifdef WV_DEV_HOOKS
 extern "C" void wv_set_tuning(int r, int s, int d, int grid) { g_tune_r = r; g_tune_s = s; g_tune_d = d; g_tune_grid = grid; }
+#endif
 
 // Scratch arena for quantised activations: a ring of slots, one per GEMV call. A slot is
 // reused only after the ring wraps, i.e. after (arena / slot) further calls.

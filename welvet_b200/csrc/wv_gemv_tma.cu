@@ -471,14 +471,15 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
     const unsigned lane4 = (unsigned)lane * 4u;
     main_loop([&](const FragT<F>& f) { return chunk_value_tbl<F>(f, xfr, tbl, lane4); });
   } else {
-    // Statistics of x that decide the width of the activation records (all CTAs see the same x and
-    // reach the same decision): A = sum over chunks of the chunk's largest magnitude, S = sum |x_j|.
-    // With 16-bit records an element is off by at most amax_chunk / 65024, so a row's error is at most
-    // sum_chunks amax_c / 65024 * sum_{j in c} |w_j|, about w_mean * 4.9e-4 * A for weights that are not
-    // concentrated on a chunk's small elements, against a budget of 1e-3 * w_mean * S. A <= S / 4 keeps
-    // an eightfold margin (N(0,1) data: A / S = 0.09); vectors with isolated outliers, inf or NaN fail
-    // the test and take 24-bit records, whose error is 2^-9 of that. Weights that sit exactly on the
-    // small elements of outlier chunks can exceed either bound: no criterion on x alone excludes that.
+    // Statistics of x that decide the width of the activation records, per warp, i.e. per 1024 columns (a warp's
+    // chunks are the same columns on every CTA and every row shard, so all of them reach the same decision):
+    // A = sum over the warp's chunks of the chunk's largest magnitude, S = sum |x_j| over the same columns.
+    // With 16-bit records an element is off by at most amax_chunk / 65024, so these columns' share of a row's error
+    // is at most sum_chunks amax_c / 65024 * sum_{j in c} |w_j|, about w_mean * 4.9e-4 * A for weights that are not
+    // concentrated on a chunk's small elements, against a budget of 1e-3 * w_mean * S. A <= S / 4 keeps an eightfold
+    // margin (N(0,1) data: A / S = 0.09); columns with isolated outliers, inf or NaN fail the test and take 24-bit
+    // records, whose error is 2^-9 of that. Weights that sit exactly on the small elements of outlier chunks can
+    // exceed either bound: no criterion on x alone excludes that.
     float xv[32];
 #pragma unroll
     for (int j = 0; j < 32; j++) xv[j] = xc[j];
@@ -491,13 +492,6 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
     float ta = amax, ts = asum;
 #pragma unroll
     for (int o = 16; o; o >>= 1) { ta += __shfl_xor_sync(0xffffffffu, ta, o); ts += __shfl_xor_sync(0xffffffffu, ts, o); }
-    // per column warp {sum of chunk maxima, sum |x|}: kept in the second half of the row-sum exchange area, which
-    // the row group writes only after its first flush barrier, i.e. after all its warps have read these
-    float2* stat = reinterpret_cast<float2*>(red + (size_t)g.nrg * g.nwc * 32) + (size_t)rg * g.nwc;
-    if (lane == 0) stat[wc] = make_float2(ta, ts);
-    asm volatile("bar.sync %0, %1;" ::"r"(rg + 1), "r"(g.nwc * 32) : "memory");
-    ta = 0.f; ts = 0.f;
-    for (int q = 0; q < g.nwc; q++) { const float2 p = stat[q]; ta += p.x; ts += p.y; }
     const bool wide = !(ta <= 0.25f * ts) || g.force3;   // NaN compares false: non-finite input takes the wide path
     if (!wide) {
       XQRegs2 xr;
@@ -577,10 +571,14 @@ static bool plane_row_bytes(const WvDevBlob& b, unsigned rb[5]) {
 }
 
 static int g_tma_rt = 0, g_tma_stages = 0;
+#ifdef WV_DEV_HOOKS
 extern "C" void wv_set_tma_tuning(int rows_per_group, int stages) { g_tma_rt = rows_per_group; g_tma_stages = stages; }
+#endif
 int wv_tma_tuning_stages() { return g_tma_stages; }
 static int g_act_width = 0;
+#ifdef WV_DEV_HOOKS
 extern "C" void wv_set_act_width(int limbs) { g_act_width = limbs; }
+#endif
 int wv_act_width() { return g_act_width; }
 int wv_tc_prequant() { return g_tma_rt == 31 ? 1 : 0; }
 

@@ -183,6 +183,22 @@ int wv_launch_unpack(const WvDevBlob& b, float* d_out, cudaStream_t st) {
   return cudaGetLastError() == cudaSuccess ? WV_OK : WV_ECUDA;
 }
 
+// quant.DecodeRow (quant/decode_row.go:7-38): one output row of the matrix as float32, the same values Unpack gives
+// for that row. Rows are counted within the rows this device holds.
+__global__ void unpack_rows_kernel(WvDevBlob b, long long first, long long count, float* __restrict__ out) {
+  const WvFmtInfo fi = wv_fmt_info(b.format);
+  long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) out[i] = wv_dequant(b, fi, first + i);
+}
+int wv_launch_unpack_rows(const WvDevBlob& b, int row, int nrows, float* d_out, cudaStream_t st) {
+  const long long count = (long long)nrows * b.cols;
+  long long nb = (count + 255) / 256;
+  if (nb > 148 * 32) nb = 148 * 32;
+  if (nb < 1) return WV_OK;
+  unpack_rows_kernel<<<(unsigned)nb, 256, 0, st>>>(b, (long long)row * b.cols, count, d_out);
+  return cudaGetLastError() == cudaSuccess ? WV_OK : WV_ECUDA;
+}
+
 // ---------------------------------------------------------------- ragged-shape GEMV
 // One warp per output row, lanes stride over columns, exact dequant + f32 multiply-add,
 // shuffle reduction. Used only when rows are not chunk aligned (cols % 32*J != 0); the

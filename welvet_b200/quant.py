@@ -160,3 +160,17 @@ def MatVec(b: Blob, x: np.ndarray, y: np.ndarray) -> None:
     ys = np.empty(b.Rows, np.float32)
     check(lib().wv_matvec(key, xs.ctypes.data, ys.ctypes.data, 1, b.Cols, b.Rows))
     y[: b.Rows] = ys
+
+
+def DecodeRow(b: Blob, row: int, dst: np.ndarray) -> None:
+    """quant.DecodeRow (quant/decode_row.go:7-38): one output row of a packed Blob into dst (len >= Cols)."""
+    if b is None:
+        raise WelvetError(_lib.WV_EFORMAT, "DecodeRow: nil blob")
+    if row < 0 or row >= b.Rows or dst.size < b.Cols:
+        raise WelvetError(_lib.WV_ESHAPE, f"quant: DecodeRow shape row={row} cols={b.Cols} dst={dst.size}")
+    if b.Format == Format.FormatNone:
+        raise WelvetError(_lib.WV_EFORMAT, "quant: DecodeRow FormatNone — use weights.DecodeRow")
+    key = EnsureResident(b)
+    out = np.empty(b.Cols, np.float32)
+    check(lib().wv_decode_row(key, row, out.ctypes.data, out.size))
+    dst[: b.Cols] = out
