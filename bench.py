@@ -13,6 +13,10 @@ reads L2-resident weights. `e2e` is the same metric through the host-pointer plu
 With N > 1 (launched by torch.distributed.run) every matrix is row-sharded across the ranks and
 each rank's kernels store their rows into every rank's output vectors (strong scaling).
 
+Beside the headline: `config4` is single-token decode of the 8B-shaped stack (32 blocks, Q4_K) on one
+GPU in tokens/s, `config5` the 70B-shaped stack (80 blocks, Q4_K) and its 128256 x 8192 LM head
+(Q8_0 and Q4_K) row-sharded over the N ranks, with the time the cross-rank ordering costs shown apart.
+
 --impl reference times the CPU restatement of the reference's SIMD path (oracle/) on the host
 cores over the same sweep: it is the reference arm, not the product. Both arms print the same
 metric, unit and config.
@@ -161,6 +165,12 @@ def run_reference(args, rank, world):
            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": desc},
            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
            "gpu_launches": 0}
+    if world == 1 and not args.quick and not args.formats and not args.no_decode:
+        for j in jobs + extra_jobs:
+            L.wv_blob_evict(j["key"])
+        decode = run_decode_configs(torch, L, _lib, stream, 0, 1, None, None)
+    if not args.quick and not args.formats and not args.no_decode:
+        out.update(decode)
     emit(out)
 
 
@@ -213,73 +223,310 @@ def parity_sample(torch, L, _lib, O, spec, w_host, x_host, rows, cols, key, y_de
     return exact, worst
 
 
-def decode_projections(torch, L, _lib, stream):
-    """Time of the projection GEMVs of one decoded token for Llama-8B shapes in Q4_K, chained as in the
-    model: 32 x [Q|K|V group, O, gate|up group, down] and the LM head followed by the greedy pick, all
-    in one CUDA graph. Norms, RoPE and attention are left out, so this is the GEMV share of a token,
-    not a tokens/s claim for the whole model."""
-    fmt, hid, ffn, kv, vocab, layers = 8, 4096, 14336, 1024, 128256, 32   # Q4_K
-    shapes = {"q": (hid, hid), "k": (kv, hid), "v": (kv, hid), "o": (hid, hid), "gate": (ffn, hid), "up": (ffn, hid), "down": (hid, ffn)}
-    key = 0x40000
-    blocks, nbytes = [], 0
-    for _ in range(2):          # two distinct blocks alternate: 286 MB of weights, more than twice L2
-        blk = {}
-        for name, (r, c) in shapes.items():
-            w = torch.randn(r * c, device="cuda") * 0.02
-            key += 1
-            _lib.check(L.wv_pack_upload_dev(key, fmt, 1, 0, w.data_ptr(), r, c, None))
-            wb = C.c_uint64()
-            _lib.check(L.wv_blob_info(key, None, None, C.byref(wb), None, None))
-            blk[name] = key
-            nbytes += int(wb.value)
-            del w
-        blocks.append(blk)
-    w = torch.randn(vocab * hid, device="cuda") * 0.02
-    key += 1
-    _lib.check(L.wv_pack_upload_dev(key, fmt, 1, 0, w.data_ptr(), vocab, hid, None))
-    del w
-    head = key
+MODELS = {
+    # BlockConfig fields, layers, vocabulary; both decode one token at position 2048 over a cache of 2048 positions
+    "8B": dict(d=4096, heads=32, kv_heads=8, head_dim=128, ffn=14336, layers=32, vocab=128256, seed=4, key=0x400000),
+    "70B": dict(d=8192, heads=64, kv_heads=8, head_dim=128, ffn=28672, layers=80, vocab=128256, seed=5, key=0x500000),
+}
+CTX = 2048
+PROJ = ("q", "k", "v", "o", "gate", "up", "down")
+
+
+def _pack_rows(torch, L, _lib, key, fmt, rows, cols, r0, r1, gen):
+    """N(0, 0.02^2) weights of the whole matrix from `gen` (every rank draws the same matrix), rows [r0, r1) packed on
+    the device under `key`; returns the packed bytes kept."""
+    w = torch.randn(rows * cols, device="cuda", generator=gen) * 0.02
+    _lib.check(L.wv_pack_upload_dev(key, fmt, 1, 0, w.data_ptr() + 4 * r0 * cols, r1 - r0, cols, None))
     wb = C.c_uint64()
-    _lib.check(L.wv_blob_info(head, None, None, C.byref(wb), None, None))
-    token_bytes = nbytes // 2 * layers + int(wb.value)
-    x = torch.randn(hid, device="cuda")
-    bufs = {n: torch.zeros(shapes[n][0], device="cuda") for n in shapes}
-    logits = torch.zeros(vocab, device="cuda")
-    pick = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _lib.check(L.wv_blob_info(key, None, None, C.byref(wb), None, None))
+    del w
+    return int(wb.value)
 
-    def multi(keys, src, dsts, outs, st):
-        n = len(keys)
-        _lib.check(L.wv_matvec_dev_multi((C.c_uint64 * n)(*keys), n, src.data_ptr(), (C.c_void_p * n)(*[d.data_ptr() for d in dsts]),
-                                         1, hid, (C.c_int * n)(*outs), st))
 
-    def token(st):
-        cur = x
-        for layer in range(layers):
-            b = blocks[layer & 1]
-            multi([b["q"], b["k"], b["v"]], cur, [bufs["q"], bufs["k"], bufs["v"]], [hid, kv, kv], st)
-            _lib.check(L.wv_matvec_dev(b["o"], bufs["q"].data_ptr(), bufs["o"].data_ptr(), 1, hid, hid, st))
-            multi([b["gate"], b["up"]], bufs["o"], [bufs["gate"], bufs["up"]], [ffn, ffn], st)
-            _lib.check(L.wv_matvec_dev(b["down"], bufs["gate"].data_ptr(), bufs["down"].data_ptr(), 1, ffn, hid, st))
-            cur = bufs["down"]
-        _lib.check(L.wv_matvec_dev(head, cur.data_ptr(), logits.data_ptr(), 1, hid, vocab, st))
-        _lib.check(L.wv_argmax_dev(logits.data_ptr(), vocab, pick.data_ptr(), st))
+class DecodeStack:
+    """A whole Llama-shaped stack for single-token decode on the device, every projection in the 4-bit k-quant and
+    row-sharded over `world` ranks. Per token: embedding row, then per block RMSNorm, Q|K|V, RoPE + cache write,
+    attention over 2049 positions, O + residual, RMSNorm, gate|up with the SiLU product, down + residual; then the
+    final RMSNorm, the LM head and the greedy pick. All blocks have their own weights and caches."""
 
+    def __init__(self, torch, L, _lib, name, head_formats, rank, world, exchange, layers=None, full_rows=False):
+        from welvet_b200.decode import BlockConfig, ShardedBlockDecoder, projection_shapes, shard_plan, vector_layout
+        from welvet_b200.dense import GatherBuffers
+        m = MODELS[name]
+        self.torch, self.L, self._lib, self.m, self.rank, self.world = torch, L, _lib, m, rank, world
+        if full_rows:                       # the unsharded twin used to check a sharded run
+            rank, world = 0, 1
+        self.srank, self.sworld = rank, world
+        self.layers = layers or m["layers"]
+        msl = CTX + 128
+        cfg = self.cfg = BlockConfig(m["d"], m["heads"], m["kv_heads"], m["head_dim"], m["ffn"], msl)
+        shapes, plan, lay = projection_shapes(cfg), shard_plan(cfg, rank, world), vector_layout(cfg)
+        self.lay = lay
+        kd, d, vocab = cfg.NumKVHeads * cfg.HeadDim, cfg.DModel, m["vocab"]
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(m["seed"])
+        t0 = time.perf_counter()
+        key = m["key"] + (0x80000 if full_rows else 0)
+        self.logits_off = lay["total"]
+        self.vec = GatherBuffers(4 * (lay["total"] + ((vocab + 63) & ~63)), rank, world, exchange)
+        self.flags = GatherBuffers(4 * (world + 2), rank, world, exchange) if world > 1 else None
+        self.local = {n: torch.zeros(sz, device="cuda") for n, sz in (("n1", d), ("n2", d), ("attn", cfg.NumHeads * cfg.HeadDim))}
+        self.gamma = torch.ones(d, device="cuda")
+        self.decs, self.keys, self.caches, self.bytes_rank = [], [], [], 0
+        # the token's embedding row: a small f32 matrix whose row 0 is fetched by the DecodeRow entry
+        emb = torch.randn(8 * d, device="cuda", generator=gen)
+        key += 1
+        self.emb_key = key
+        _lib.check(L.wv_pack_upload_dev(key, 0, 1, 0, emb.data_ptr(), 8, d, None))
+        for layer in range(self.layers):
+            keys = {}
+            for pname in PROJ:
+                key += 1
+                r, c = shapes[pname]
+                self.bytes_rank += _pack_rows(torch, L, _lib, key, 8, r, c, plan[pname][0], plan[pname][1], gen)
+                keys[pname] = key
+            ck = torch.randn(msl, kd, device="cuda", generator=gen)
+            cv = torch.randn(msl, kd, device="cuda", generator=gen)
+            self.caches.append((ck, cv))
+            ptrs = {n: t.data_ptr() for n, t in self.local.items()}
+            ptrs.update(attn_norm=self.gamma.data_ptr(), ffn_norm=self.gamma.data_ptr(), cache_k=ck.data_ptr(), cache_v=cv.data_ptr())
+            self.decs.append(ShardedBlockDecoder(cfg, keys, ptrs, rank, world, self.vec, self.flags))
+            self.keys.append(keys)
+        self.heads = {}
+        self.h0, self.h1 = vocab * rank // world, vocab * (rank + 1) // world
+        for hname, hfmt in head_formats:
+            key += 1
+            self.heads[hname] = (key, hfmt, _pack_rows(torch, L, _lib, key, hfmt, vocab, d, self.h0, self.h1, gen))
+        self.last_key = key
+        self.pick = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.flags_all = (C.c_void_p * world)(*self.flags.ptrs) if world > 1 else None
+        self.logits_all = self.vec.pointers(self.logits_off)
+        torch.cuda.synchronize()
+        self.setup_s = time.perf_counter() - t0
+
+    def sync(self, st):
+        if self.sworld > 1:
+            self._lib.check(self.L.wv_gather_signal(self.flags_all, self.sworld, self.srank, st))
+            self._lib.check(self.L.wv_gather_wait(self.flags.own, self.sworld, st))
+
+    def token(self, st, head=None, flags=True, blocks=None):
+        L, chk, cfg, d = self.L, self._lib.check, self.cfg, self.cfg.DModel
+        ha = self.vec.own + 4 * self.lay["ha"]
+        chk(L.wv_decode_row_dev(self.emb_key, 0, ha, st))
+        for dec in self.decs[:blocks]:
+            dec.step(CTX, st, flags)
+        if head is None:
+            return
+        chk(L.wv_rmsnorm_dev(ha, self.gamma.data_ptr(), self.local["n1"].data_ptr(), 1, d, cfg.Eps, st))
+        chk(L.wv_matvec_dev_gather(self.heads[head][0], self.local["n1"].data_ptr(), self.logits_all, self.sworld, self.srank, self.h0,
+                                   d, self.h1 - self.h0, st))
+        if flags:
+            self.sync(st)
+        chk(L.wv_argmax_dev(self.vec.own + 4 * self.logits_off, self.m["vocab"], self.pick.data_ptr(), st))
+
+    def launches_per_token(self):
+        return 1 + self.layers * self.decs[0].launches_per_step() + (5 if self.sworld > 1 else 3)
+
+    def hidden(self):
+        return self.vec.read(self.lay["ha"], self.cfg.DModel)
+
+    def close(self):
+        for keys in self.keys:
+            for k in keys.values():
+                self.L.wv_blob_evict(k)
+        self.L.wv_blob_evict(self.emb_key)
+        for k, _, _ in self.heads.values():
+            self.L.wv_blob_evict(k)
+        self.decs, self.caches = [], []
+
+
+def _timed_graph(torch, stream, dist, fn, reps=5):
+    """Run fn once (first launches set kernel attributes), capture it, time the replays on the device; max over ranks."""
     with torch.cuda.stream(stream):
-        token(stream.cuda_stream)
+        fn(stream.cuda_stream)
     stream.synchronize()
+    if dist is not None:
+        dist.barrier()
     g = torch.cuda.CUDAGraph()
     with torch.cuda.graph(g, stream=stream):
-        token(torch.cuda.current_stream().cuda_stream)
-    best = time_graph(torch, stream, g)
+        fn(torch.cuda.current_stream().cuda_stream)
+    if dist is not None:
+        dist.barrier()
+    ms = time_graph(torch, stream, g, reps)
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
     del g
-    for blk in blocks:
-        for k in blk.values():
+    return ms
+
+
+def _allsum(torch, dist, v):
+    if dist is None:
+        return v
+    t = torch.tensor([float(v)], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t)
+    return float(t.item())
+
+
+def decode_tokens(torch, L, _lib, stream, stack, dist):
+    """tokens/s of the stack per LM-head format: one CUDA graph per token; sharded runs are also timed without the
+    signal / wait kernels (the ranks then run unordered and the values are not meaningful) to show what the ordering costs."""
+    out = {"model": "%d blocks (d_model %d, %d/%d heads of %d, FFN %d), LM head %dx%d; position %d over a cache of %d positions" % (
+               stack.layers, stack.cfg.DModel, stack.cfg.NumHeads, stack.cfg.NumKVHeads, stack.cfg.HeadDim, stack.cfg.IntermediateDim,
+               stack.m["vocab"], stack.cfg.DModel, CTX, CTX),
+           "format": "Q4_K", "weights": "N(0,0.02^2) seed %d, every block its own matrices and caches" % stack.m["seed"],
+           "setup_s": round(stack.setup_s, 1), "launches_per_token": stack.launches_per_token(), "heads": {}}
+    for hname, (hkey, hfmt, hbytes) in stack.heads.items():
+        row = {}
+        ms = _timed_graph(torch, stream, dist, lambda st: stack.token(st, hname, True))
+        row["ms_per_token"] = round(ms, 4)
+        row["tokens_per_s"] = round(1e3 / ms, 2)
+        tok_bytes = _allsum(torch, dist, stack.bytes_rank + hbytes)
+        row["packed_bytes_per_token"] = int(tok_bytes)
+        row["gbs"] = round(tok_bytes / ms / 1e6, 1)
+        row["pick"] = int(stack.pick.item())
+        if stack.sworld > 1:
+            ms2 = _timed_graph(torch, stream, dist, lambda st: stack.token(st, hname, False))
+            row["ms_per_token_without_flag_kernels"] = round(ms2, 4)
+            row["ordering_ms"] = round(ms - ms2, 4)
+        out["heads"][hname] = row
+    out["device_status"] = int(L.wv_device_status())
+    return out
+
+
+def lm_head_sweep(torch, L, _lib, stream, stack, dist):
+    """The row-sharded LM head alone (128256 x d_model), per format: a graph of back-to-back launches rotating over
+    enough device copies of this rank's rows that no launch reads L2-resident weights; sharded, every launch is
+    followed by the arrival flags, and a second timing leaves them out."""
+    m, d, vocab = stack.m, stack.cfg.DModel, stack.m["vocab"]
+    x = torch.randn(d, device="cuda")
+    res = {}
+    key = stack.last_key + 0x1000
+    for hname, (hkey, hfmt, hbytes) in stack.heads.items():
+        K = max(1, int(np.ceil(300e6 / hbytes)))
+        keys = [hkey]
+        gen = torch.Generator(device="cuda")
+        for k in range(1, K):
+            gen.manual_seed(1000 + k)
+            key += 1
+            _pack_rows(torch, L, _lib, key, hfmt, vocab, d, stack.h0, stack.h1, gen)
+            keys.append(key)
+        n_l = max(8, 4 * K)
+
+        def run(st, flags):
+            for i in range(n_l):
+                _lib.check(L.wv_matvec_dev_gather(keys[i % K], x.data_ptr(), stack.logits_all, stack.sworld, stack.srank, stack.h0, d,
+                                                  stack.h1 - stack.h0, st))
+                if flags:
+                    stack.sync(st)
+        us = _timed_graph(torch, stream, dist, lambda st: run(st, True)) / n_l * 1e3
+        full = _allsum(torch, dist, hbytes)
+        row = {"rows": vocab, "cols": d, "packed_bytes": int(full), "us": round(us, 2), "gbs": round(full / us / 1e3, 1),
+               "frac_8TBs_per_gpu": round(full / us / 1e3 / NOMINAL_HBM_GBS / stack.world, 3), "copies_rotated": K}
+        if stack.sworld > 1:
+            us2 = _timed_graph(torch, stream, dist, lambda st: run(st, False)) / n_l * 1e3
+            row["us_kernel_only"] = round(us2, 2)
+            row["us_ordering"] = round(us - us2, 2)
+        for k in keys[1:]:
             L.wv_blob_evict(k)
-    L.wv_blob_evict(head)
-    return {"model": "Llama-8B shapes (32 blocks: Q|K|V, O, gate|up, down; LM head 128256x4096; greedy pick)", "format": "Q4_K",
-            "launches_per_token": layers * 4 + 2, "packed_bytes_per_token": token_bytes, "ms_per_token": round(best, 4),
-            "gbs": round(token_bytes / best / 1e6, 1), "tokens_per_s_gemv_only": round(1e3 / best, 1),
-            "note": "projection GEMVs and the pick only; norms, RoPE and attention are not timed"}
+        res[hname] = row
+    return res
+
+
+def block0_parity(torch, L, _lib, O, stack):
+    """One block of the stack against the reference's host arithmetic: float64 RMSNorm, RoPE, attention and SiLU
+    product from the oracle around f32 GEMVs over the dequantised weights the device holds (whose bit-exactness
+    against the oracle's Unpack the per-format table reports). Returns max |h - h_ref| / max |h_ref|."""
+    from welvet_b200.decode import projection_shapes
+    cfg, d = stack.cfg, stack.cfg.DModel
+    shapes = projection_shapes(cfg)
+    W = {}
+    for pname in PROJ:
+        r, c = shapes[pname]
+        w = np.empty(r * c, np.float32)
+        _lib.check(L.wv_unpack(stack.keys[0][pname], w.ctypes.data))
+        W[pname] = w.reshape(r, c)
+    x = np.empty(d, np.float32)
+    _lib.check(L.wv_decode_row(stack.emb_key, 0, x.ctypes.data, d))
+    ck, cv = (t.cpu().numpy().astype(np.float64) for t in stack.caches[0])
+    g = np.ones(d, np.float32)
+    n1 = O.rmsnorm(x, g)
+    q, k, v = (W[n] @ n1 for n in ("q", "k", "v"))
+    qr = O.rope(q, CTX, cfg.NumHeads, cfg.HeadDim)
+    ck[CTX % cfg.MaxSeqLen] = O.rope(k, CTX, cfg.NumKVHeads, cfg.HeadDim)
+    cv[CTX % cfg.MaxSeqLen] = v
+    attn = O.attn_decode(qr, ck, cv, cfg.NumHeads, cfg.NumKVHeads, cfg.HeadDim, CTX + 1, cfg.MaxSeqLen).astype(np.float32)
+    h1 = x + W["o"] @ attn
+    n2 = O.rmsnorm(h1, g)
+    ref = h1 + W["down"] @ O.silu_mul(W["gate"] @ n2, W["up"] @ n2)
+    stack.token(None, None, True, blocks=1)
+    torch.cuda.synchronize()
+    got = stack.hidden()
+    return float(np.max(np.abs(got - ref)) / np.max(np.abs(ref)))
+
+
+def sharded_chain_check(torch, L, _lib, stack, exchange_none, dist):
+    """The sharded stack against its unsharded twin on this rank: the hidden state after two blocks must agree bit
+    for bit (each output row is computed by the same code whatever rank holds it), and every rank must hold the same
+    hidden state, logits and pick after a whole token."""
+    twin = DecodeStack(torch, L, _lib, "70B" if stack.m is MODELS["70B"] else "8B", [], stack.rank, stack.world, None, layers=2, full_rows=True)
+    twin.token(None, None, True)
+    stack.token(None, None, True, blocks=2)
+    torch.cuda.synchronize()
+    same = bool(np.array_equal(twin.hidden().view(np.uint32), stack.hidden().view(np.uint32)))
+    twin.close()
+    twin.vec.close()
+    dist.barrier()
+    hname = next(iter(stack.heads))
+    stack.token(None, hname, True)
+    torch.cuda.synchronize()
+    dist.barrier()
+    logits = torch.from_numpy(stack.vec.read(stack.logits_off, stack.m["vocab"])).cuda()
+    mine = torch.cat([torch.from_numpy(stack.hidden()).cuda(), logits, stack.pick.float()])
+    ref = mine.clone()
+    dist.broadcast(ref, 0)
+    same = same and bool(torch.equal(mine.view(torch.int32), ref.view(torch.int32)))
+    t = torch.tensor([1.0 if same else 0.0], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return bool(t.item() == 1.0)
+
+
+def run_decode_configs(torch, L, _lib, stream, rank, world, exchange, dist):
+    """The decode configurations beside the headline sweep: the 8B stack on one GPU (tokens/s, one block checked against
+    the reference's host arithmetic) and the 70B stack with its LM head as Q8_0 and Q4_K, row-sharded over the ranks."""
+    res = {}
+    if world == 1:
+        st8 = DecodeStack(torch, L, _lib, "8B", [("Q4_K", 8)], 0, 1, None)
+        c4 = decode_tokens(torch, L, _lib, stream, st8, None)
+        import oracle as O
+        c4["block0_max_rel_vs_host_arithmetic"] = float("%.3e" % block0_parity(torch, L, _lib, O, st8))
+        st8.close()
+        st8.vec.close()
+        del st8
+        torch.cuda.empty_cache()
+        res["config4"] = c4
+    st70 = DecodeStack(torch, L, _lib, "70B", [("Q8_0", 1), ("Q4_K", 8)], rank, world, exchange)
+    c5 = {"n_gpus": world, "lm_head": lm_head_sweep(torch, L, _lib, stream, st70, dist),
+          "stack": decode_tokens(torch, L, _lib, stream, st70, dist),
+          "sharding": "rows of every projection and of the LM head split evenly over the ranks; each rank's kernels store their rows into "
+                      "every rank's vectors over NVLink (peer mappings), ordered by arrival flags on the device; norms, RoPE, the cache "
+                      "and attention run replicated" if world > 1 else "single GPU"}
+    if world > 1:
+        c5["sharded_equals_unsharded"] = sharded_chain_check(torch, L, _lib, st70, None, dist)
+        torch.cuda.synchronize()
+        dist.barrier()
+        st70.vec.close_peers()
+        st70.flags.close_peers()
+        torch.cuda.synchronize()
+        dist.barrier()
+    st70.close()
+    st70.vec.free_own()
+    if st70.flags is not None:
+        st70.flags.free_own()
+    res["config5"] = c5
+    return res
 
 
 def main():
@@ -296,6 +543,7 @@ def main():
     ap.add_argument("--impl", default="welvet_b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the per-format parity fields")
+    ap.add_argument("--no-decode", action="store_true", help="skip the whole-stack decode runs (8B block stack, 70B row-sharded stack and LM head)")
     ap.add_argument("--formats", default="", help="comma list: restrict the sweep (for profiler captures)")
     ap.add_argument("--quick", action="store_true", help="skip the per-format table, the e2e and the CPU legs (profiler captures)")
     args = ap.parse_args()
@@ -465,6 +713,11 @@ def main():
         dist.barrier()
         gbufs.free_own()
         gflags.free_own()
+        for j in jobs:
+            L.wv_blob_evict(j["key"])
+        decode = None
+        if not args.quick and not args.formats and not args.no_decode:
+            decode = run_decode_configs(torch, L, _lib, stream, rank, world, exchange, dist)
         dist.destroy_process_group()
     if rank != 0:
         return
@@ -588,8 +841,12 @@ def main():
         gbs, cores, sec, total = cpu_leg(3, 1, sample, SHAPES[:1])
         out["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
                                "sample": f"{len(sample)} formats ({','.join(f[0] for f in sample)}) at 4096x14336, 3 timed passes, SIMD-path caches prebuilt"}
-    if world == 1 and not args.quick and not args.formats:
-        out["decode_projections"] = decode_projections(torch, L, _lib, stream)
+    if world == 1 and not args.quick and not args.formats and not args.no_decode:
+        for j in jobs + extra_jobs:
+            L.wv_blob_evict(j["key"])
+        decode = run_decode_configs(torch, L, _lib, stream, 0, 1, None, None)
+    if not args.quick and not args.formats and not args.no_decode:
+        out.update(decode)
     emit(out)
 
 

@@ -7,6 +7,7 @@
 // decide a normalisation are kept in float64 and the rest is float32.
 #include "wv_common.cuh"
 #include <math.h>
+#include <stdlib.h>
 
 // ------------------------------------------------------------------ RMSNorm
 // y[i] = x[i] * inv * gamma[i], inv = 1 / sqrt(sum(x^2) / dim + eps)  (rmsnorm/cpu.go:76-85).
@@ -101,142 +102,254 @@ int wv_launch_rope_cache(float* dq, const float* dk, const float* dv, float* dca
 // attnForward (mha/attn.go:15-120) for seqLen 1 under the causal mask: the query at position
 // kv_len - 1 sees cache rows 0 .. kv_len-1 (row kPos lives in slot kPos % msl), grouped-query heads
 // share kv head h / (heads / kv_heads), scores = q.k * scale, max-subtracted softmax, out = sum w v.
-// One CTA per (query head, split of the positions); the splits' partial results {max, sum, acc[head_dim]}
-// are merged by the last split to finish (a counter per head, no waiting). head_dim <= 256, multiple of 4.
+//
+// Two launches. attn_split_kernel: one CTA per (group of GC query heads that share a kv head, split of the
+// positions), about two CTAs per SM; a K or V row is read once for the GC heads, a warp's K rows are all in flight
+// together and its first V rows are requested before the softmax of the scores. Each CTA leaves one record
+// {max, sum, acc[head_dim]} per head. attn_merge_kernel: one CTA per head, one thread per dimension, merges the
+// records in split order (the result does not depend on the order the CTAs ran in) with every load of a batch of
+// splits in flight at once. Every step of this kernel pair is a round trip to L2, so the structure is chosen to
+// keep their number small: q, K, (V), records out | records in, result out. head_dim <= 256, multiple of 4.
 #define ATT_THREADS 256
-#define ATT_MAX_CHUNK 4096   // positions per split held in shared memory
-__global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const float* __restrict__ q, const float* __restrict__ cache_k,
-                                                                  const float* __restrict__ cache_v, float* __restrict__ out,
-                                                                  float* __restrict__ part, unsigned* __restrict__ counters,
-                                                                  int num_heads, int num_kv_heads, int head_dim, int kv_len, int msl,
-                                                                  float scale, int nsplit) {
-  __shared__ float s_score[ATT_MAX_CHUNK];
-  __shared__ float s_red[ATT_THREADS / 32];
-  __shared__ float s_acc[ATT_THREADS / 32][256];
-  __shared__ float s_bcast[2];
-  __shared__ unsigned s_last;
+#define ATT_WARPS (ATT_THREADS / 32)
+#define ATT_CHUNK 256        // positions per split at most
+#define ATT_MERGE_BATCH 40
+template <int GC, bool WIDE>
+__global__ void __launch_bounds__(ATT_THREADS, 2) attn_split_kernel(const float* __restrict__ q, const float* __restrict__ cache_k,
+                                                                 const float* __restrict__ cache_v, float* __restrict__ out,
+                                                                 float* __restrict__ part, int num_heads, int num_kv_heads,
+                                                                 int head_dim, int kv_len, int msl, float scale, int nsplit) {
+  constexpr int UN = WIDE ? 4 : 8;                        // rows a warp has in flight
+  constexpr bool EARLY_V = GC * (WIDE ? 2 : 1) <= 4;       // registers allow requesting the first V rows before the softmax
+  extern __shared__ __align__(16) float att_smem[];
+  float* s_score = att_smem;                              // [GC][ATT_CHUNK]
+  float* s_acc = att_smem + GC * ATT_CHUNK;               // [ATT_WARPS][GC][head_dim]
+  __shared__ float s_max[GC], s_sum[GC];
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const int h = blockIdx.x, sp = blockIdx.y;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = ATT_THREADS / 32;
-  const int kvh = h / (num_heads / num_kv_heads);
+  const int grp = blockIdx.x, sp = blockIdx.y;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int h0 = grp * GC;
+  const int kvh = h0 / (num_heads / num_kv_heads);
   const int kv_dim = num_kv_heads * head_dim;
   const int per = (kv_len + nsplit - 1) / nsplit;
   const int p0 = sp * per, p1 = min(kv_len, p0 + per);
   const int n = max(0, p1 - p0);
   const int vec = head_dim >> 2;           // float4 per row; lanes beyond it idle
-  const float* qh = q + (size_t)h * head_dim;
-  float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), qv2 = qv;
-  if (lane < vec) qv = reinterpret_cast<const float4*>(qh)[lane];
-  if (lane + 32 < vec) qv2 = reinterpret_cast<const float4*>(qh)[lane + 32];
-  // scores of this split's positions, one warp per position
-  float lmax = -3.0e38f;
-  for (int i = warp; i < n; i += nwarp) {
-    const float4* kr = reinterpret_cast<const float4*>(cache_k + (size_t)((p0 + i) % msl) * kv_dim + (size_t)kvh * head_dim);
-    float d = 0.f;
-    if (lane < vec) { const float4 kk = kr[lane]; d = qv.x * kk.x + qv.y * kk.y + qv.z * kk.z + qv.w * kk.w; }
-    if (lane + 32 < vec) { const float4 kk = kr[lane + 32]; d += qv2.x * kk.x + qv2.y * kk.y + qv2.z * kk.z + qv2.w * kk.w; }
+  const bool on0 = lane < vec, on1 = WIDE && lane + 32 < vec;
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  auto row_of = [&](const float* cache, int i) {
+    return reinterpret_cast<const float4*>(cache + (size_t)((p0 + min(i, max(n - 1, 0))) % msl) * kv_dim + (size_t)kvh * head_dim);
+  };
+  float4 vv[UN], vw[WIDE ? UN : 1];          // V rows of the warp's first positions, requested early
+  {
+    // scores: a warp takes positions warp, warp + 8, ...
+    float4 qv[GC], qw[WIDE ? GC : 1];
 #pragma unroll
-    for (int o = 16; o; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-    d *= scale;
-    if (lane == 0) s_score[i] = d;
-    lmax = fmaxf(lmax, d);
-  }
-  if (lane == 0) s_red[warp] = lmax;
-  __syncthreads();
-  if (tid == 0) { float m = s_red[0]; for (int w = 1; w < nwarp; w++) m = fmaxf(m, s_red[w]); s_bcast[0] = m; }
-  __syncthreads();
-  const float m = s_bcast[0];
-  float lsum = 0.f;
-  for (int i = tid; i < n; i += ATT_THREADS) { const float e = __expf(s_score[i] - m); s_score[i] = e; lsum += e; }
-#pragma unroll
-  for (int o = 16; o; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
-  if (lane == 0) s_red[warp] = lsum;
-  __syncthreads();
-  if (tid == 0) { float t = 0.f; for (int w = 0; w < nwarp; w++) t += s_red[w]; s_bcast[1] = t; }
-  // weighted sum of the V rows: a warp walks its positions, a lane keeps its 4 (+4) dimensions
-  float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
-  for (int i = warp; i < n; i += nwarp) {
-    const float w = s_score[i];
-    const float4* vr = reinterpret_cast<const float4*>(cache_v + (size_t)((p0 + i) % msl) * kv_dim + (size_t)kvh * head_dim);
-    if (lane < vec) { const float4 vv = vr[lane]; a0.x += w * vv.x; a0.y += w * vv.y; a0.z += w * vv.z; a0.w += w * vv.w; }
-    if (lane + 32 < vec) { const float4 vv = vr[lane + 32]; a1.x += w * vv.x; a1.y += w * vv.y; a1.z += w * vv.z; a1.w += w * vv.w; }
-  }
-  if (lane < vec) { float* d = &s_acc[warp][lane * 4]; d[0] = a0.x; d[1] = a0.y; d[2] = a0.z; d[3] = a0.w; }
-  if (lane + 32 < vec) { float* d = &s_acc[warp][(lane + 32) * 4]; d[0] = a1.x; d[1] = a1.y; d[2] = a1.z; d[3] = a1.w; }
-  __syncthreads();
-  const float ssum = s_bcast[1];
-  // this split's record: [0] max, [1] sum, [2 ..] unnormalised accumulators
-  float* rec = part + ((size_t)h * nsplit + sp) * (head_dim + 2);
-  if (tid < head_dim) {
-    float t = 0.f;
-    for (int w = 0; w < nwarp; w++) t += s_acc[w][tid];
-    if (nsplit == 1) { out[(size_t)h * head_dim + tid] = n > 0 ? t / ssum : 0.f; }
-    else rec[2 + tid] = t;
-  }
-  if (nsplit == 1) return;
-  if (tid == 0) { rec[0] = n > 0 ? m : -3.0e38f; rec[1] = n > 0 ? ssum : 0.f; }
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const unsigned prev = atomicAdd(&counters[h], 1u);
-    s_last = (prev == (unsigned)nsplit - 1u);
-    if (s_last) counters[h] = 0u;   // ready for the next launch
-  }
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-  // merge in split order (fixed order: the result does not depend on which split finished last)
-  const float* base = part + (size_t)h * nsplit * (head_dim + 2);
-  float gm = -3.0e38f;
-  for (int s = 0; s < nsplit; s++) gm = fmaxf(gm, __ldcg(base + (size_t)s * (head_dim + 2)));
-  if (tid < head_dim) {
-    float tot = 0.f, acc = 0.f;
-    for (int s = 0; s < nsplit; s++) {
-      const float* r = base + (size_t)s * (head_dim + 2);
-      const float f = __expf(__ldcg(r) - gm);
-      tot += f * __ldcg(r + 1);
-      acc += f * __ldcg(r + 2 + tid);
+    for (int g = 0; g < GC; g++) {
+      const float4* qh = reinterpret_cast<const float4*>(q + (size_t)(h0 + g) * head_dim);
+      qv[g] = on0 ? qh[lane] : zero4;
+      if (WIDE) qw[g] = on1 ? qh[lane + 32] : zero4;
     }
-    out[(size_t)h * head_dim + tid] = tot > 0.f ? acc / tot : 0.f;
+    for (int i0 = warp; i0 < n; i0 += ATT_WARPS * UN) {
+      float4 kk[UN], kw[WIDE ? UN : 1];
+#pragma unroll
+      for (int u = 0; u < UN; u++) {
+        const float4* kr = row_of(cache_k, i0 + u * ATT_WARPS);
+        kk[u] = on0 ? kr[lane] : zero4;
+        if (WIDE) kw[u] = on1 ? kr[lane + 32] : zero4;
+      }
+      if (EARLY_V && i0 == warp) {
+#pragma unroll
+        for (int u = 0; u < UN; u++) {
+          const float4* vr = row_of(cache_v, i0 + u * ATT_WARPS);
+          vv[u] = on0 ? vr[lane] : zero4;
+          if (WIDE) vw[u] = on1 ? vr[lane + 32] : zero4;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UN; u++) {
+        const int i = i0 + u * ATT_WARPS;
+#pragma unroll
+        for (int g = 0; g < GC; g++) {
+          float d = qv[g].x * kk[u].x + qv[g].y * kk[u].y + qv[g].z * kk[u].z + qv[g].w * kk[u].w;
+          if (WIDE) d += qw[g].x * kw[u].x + qw[g].y * kw[u].y + qw[g].z * kw[u].z + qw[g].w * kw[u].w;
+#pragma unroll
+          for (int o = 16; o; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+          if (lane == 0 && i < n) s_score[g * ATT_CHUNK + i] = d * scale;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  // max-subtracted exponentials: warp g takes head g
+  for (int g = warp; g < GC; g += ATT_WARPS) {
+    float m = -3.0e38f;
+    for (int i = lane; i < n; i += 32) m = fmaxf(m, s_score[g * ATT_CHUNK + i]);
+#pragma unroll
+    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float t = 0.f;
+    for (int i = lane; i < n; i += 32) { const float e = __expf(s_score[g * ATT_CHUNK + i] - m); s_score[g * ATT_CHUNK + i] = e; t += e; }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) { s_max[g] = m; s_sum[g] = t; }
+  }
+  __syncthreads();
+  {
+    // weighted sum of the V rows: a lane keeps its 4 (+4) dimensions of every head
+    float4 a0[GC], a1[WIDE ? GC : 1];
+#pragma unroll
+    for (int g = 0; g < GC; g++) { a0[g] = zero4; if (WIDE) a1[g] = zero4; }
+    for (int i0 = warp; i0 < n; i0 += ATT_WARPS * UN) {
+      if (!EARLY_V || i0 != warp) {
+#pragma unroll
+        for (int u = 0; u < UN; u++) {
+          const float4* vr = row_of(cache_v, i0 + u * ATT_WARPS);
+          vv[u] = on0 ? vr[lane] : zero4;
+          if (WIDE) vw[u] = on1 ? vr[lane + 32] : zero4;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UN; u++) {
+        const int i = i0 + u * ATT_WARPS;
+        if (i < n) {
+#pragma unroll
+          for (int g = 0; g < GC; g++) {
+            const float w = s_score[g * ATT_CHUNK + i];
+            a0[g].x += w * vv[u].x; a0[g].y += w * vv[u].y; a0[g].z += w * vv[u].z; a0[g].w += w * vv[u].w;
+            if (WIDE) { a1[g].x += w * vw[u].x; a1[g].y += w * vw[u].y; a1[g].z += w * vw[u].z; a1[g].w += w * vw[u].w; }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < GC; g++) {
+      float4* d = reinterpret_cast<float4*>(s_acc + ((size_t)warp * GC + g) * head_dim);
+      if (on0) d[lane] = a0[g];
+      if (WIDE) { if (on1) d[lane + 32] = a1[g]; }
+    }
+  }
+  __syncthreads();
+  // this split's records, one per head: [0] max, [1] sum, [2 ..] unnormalised accumulators (warps summed in order)
+  for (int e = tid; e < GC * head_dim; e += ATT_THREADS) {
+    const int g = e / head_dim, dim = e - g * head_dim;
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; w++) t += s_acc[((size_t)w * GC + g) * head_dim + dim];
+    if (nsplit == 1) out[(size_t)(h0 + g) * head_dim + dim] = n > 0 ? t / s_sum[g] : 0.f;
+    else part[((size_t)(h0 + g) * nsplit + sp) * (head_dim + 2) + 2 + dim] = t;
+  }
+  if (nsplit > 1 && tid < GC) {
+    float* rec = part + ((size_t)(h0 + tid) * nsplit + sp) * (head_dim + 2);
+    rec[0] = n > 0 ? s_max[tid] : -3.0e38f;
+    rec[1] = n > 0 ? s_sum[tid] : 0.f;
   }
 }
 
-// Scratch of the split merge: nsplit records per head and one counter per head, owned by the library.
+// Merge of the splits' records of one head (blockIdx.x), one thread per dimension, in split order.
+__global__ void __launch_bounds__(256) attn_merge_kernel(const float* __restrict__ part, float* __restrict__ out, int head_dim, int nsplit) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int h = blockIdx.x, dim = threadIdx.x;
+  if (dim >= head_dim) return;
+  const float* base = part + (size_t)h * nsplit * (head_dim + 2);
+  float gm = -3.0e38f, tot = 0.f, acc = 0.f;
+  for (int s0 = 0; s0 < nsplit; s0 += ATT_MERGE_BATCH) {
+    float m[ATT_MERGE_BATCH], t[ATT_MERGE_BATCH], v[ATT_MERGE_BATCH];
+#pragma unroll
+    for (int u = 0; u < ATT_MERGE_BATCH; u++) {
+      const bool on = s0 + u < nsplit;
+      const float* r = base + (size_t)(on ? s0 + u : s0) * (head_dim + 2);
+      m[u] = on ? r[0] : -3.0e38f;
+      t[u] = on ? r[1] : 0.f;
+      v[u] = on ? r[2 + dim] : 0.f;
+    }
+    float bm = gm;
+#pragma unroll
+    for (int u = 0; u < ATT_MERGE_BATCH; u++) bm = fmaxf(bm, m[u]);
+    const float resc = __expf(gm - bm);     // 1 for the first batch's gm = -3e38 start as well: tot and acc are 0 then
+    tot *= resc; acc *= resc; gm = bm;
+#pragma unroll
+    for (int u = 0; u < ATT_MERGE_BATCH; u++) {
+      const float f = __expf(m[u] - gm);
+      tot += f * t[u];
+      acc += f * v[u];
+    }
+  }
+  out[(size_t)h * head_dim + dim] = tot > 0.f ? acc / tot : 0.f;
+}
+
+// Records of the splits: nsplit per head, owned by the library.
 static float* g_att_part = nullptr;
-static unsigned* g_att_cnt = nullptr;
 static size_t g_att_part_floats = 0;
-static int g_att_heads = 0;
+
+template <int GC, bool WIDE>
+static int attn_launch(cudaLaunchConfig_t& cfg, size_t smem, const float* dq, const float* dk, const float* dv, float* dout, int num_heads,
+                       int num_kv_heads, int head_dim, int kv_len, int msl, float scale, int nsplit) {
+  static unsigned attr_mask = 0;   // per device: opt in to more than 48 KB of dynamic shared memory once
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (smem > 48 * 1024 && !(attr_mask & (1u << (dev & 31)))) {
+    if (cudaFuncSetAttribute(attn_split_kernel<GC, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return WV_ECUDA;
+    attr_mask |= 1u << (dev & 31);
+  }
+  cfg.dynamicSmemBytes = smem;
+  return cudaLaunchKernelEx(&cfg, attn_split_kernel<GC, WIDE>, dq, dk, dv, dout, g_att_part, num_heads, num_kv_heads, head_dim,
+                            kv_len, msl, scale, nsplit) == cudaSuccess ? WV_OK : WV_ECUDA;
+}
 
 int wv_launch_attn_decode(const float* dq, const float* dcache_k, const float* dcache_v, float* dout, int num_heads, int num_kv_heads,
                           int head_dim, int kv_len, int msl, float scale, cudaStream_t st) {
   if (head_dim > 256 || (head_dim & 3) || num_heads % num_kv_heads) { wv_set_error("attention: head_dim %d / heads %d:%d not supported", head_dim, num_heads, num_kv_heads); return WV_ESHAPE; }
-  // splits: enough CTAs to fill the SMs, each holding at most ATT_MAX_CHUNK positions
-  int nsplit = 1;
-  while (nsplit < 16 && (num_heads * nsplit < 128 || (kv_len + nsplit - 1) / nsplit > ATT_MAX_CHUNK) && kv_len / (nsplit * 2) >= 64) nsplit *= 2;
-  while ((kv_len + nsplit - 1) / nsplit > ATT_MAX_CHUNK) nsplit *= 2;
-  if (nsplit > 1024) { wv_set_error("attention: kv_len %d too long", kv_len); return WV_ESHAPE; }
+  // query heads per CTA: the largest power of two <= 8 that divides the group of heads sharing a kv head
+  const int G = num_heads / num_kv_heads;
+  int gc = 1;
+  while (gc < 8 && G % (gc * 2) == 0) gc *= 2;
+  const int ngroups = num_heads / gc;
+  // splits: about two CTAs per SM, at least 8 positions and at most ATT_CHUNK positions each
+  int ctas = 2 * 148;
+#ifdef WV_DEV_HOOKS
+  if (const char* e = getenv("WV_ATT_CTAS")) ctas = atoi(e);
+#endif
+  int nsplit = (ctas + ngroups - 1) / ngroups;
+  if (nsplit > kv_len / 8) nsplit = kv_len / 8;
+  if (nsplit < 1) nsplit = 1;
+  if ((kv_len + nsplit - 1) / nsplit > ATT_CHUNK) nsplit = (kv_len + ATT_CHUNK - 1) / ATT_CHUNK;
+  if (nsplit > 65536) { wv_set_error("attention: kv_len %d too long", kv_len); return WV_ESHAPE; }
   const size_t need = (size_t)num_heads * nsplit * (head_dim + 2);
-  if (need > g_att_part_floats || num_heads > g_att_heads) {
+  if (need > g_att_part_floats) {
     // grows only when a larger shape arrives (set-up time: not capturable)
     cudaStreamSynchronize(st);
     if (g_att_part) cudaFree(g_att_part);
-    if (g_att_cnt) cudaFree(g_att_cnt);
-    g_att_part = nullptr; g_att_cnt = nullptr;
+    g_att_part = nullptr;
     const size_t want = need * 2;
-    const int heads = num_heads > 256 ? num_heads : 256;
-    if (cudaMalloc(&g_att_part, want * 4) != cudaSuccess || cudaMalloc(&g_att_cnt, (size_t)heads * 4) != cudaSuccess) { cudaGetLastError(); wv_set_error("attention: scratch allocation failed"); return WV_ENOMEM; }
-    cudaMemset(g_att_cnt, 0, (size_t)heads * 4);
-    g_att_part_floats = want; g_att_heads = heads;
+    if (cudaMalloc(&g_att_part, want * 4) != cudaSuccess) { cudaGetLastError(); g_att_part_floats = 0; wv_set_error("attention: scratch allocation failed"); return WV_ENOMEM; }
+    g_att_part_floats = want;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(num_heads, nsplit); cfg.blockDim = dim3(ATT_THREADS); cfg.stream = st;
+  cfg.gridDim = dim3(ngroups, nsplit); cfg.blockDim = dim3(ATT_THREADS); cfg.stream = st;
   cudaLaunchAttribute at[1];
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at; cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, attn_decode_kernel, dq, dcache_k, dcache_v, dout, g_att_part, g_att_cnt, num_heads, num_kv_heads, head_dim,
-                            kv_len, msl, scale, nsplit) == cudaSuccess ? WV_OK : WV_ECUDA;
+  const size_t smem = ((size_t)gc * ATT_CHUNK + (size_t)ATT_WARPS * gc * head_dim) * sizeof(float);
+  const bool wide = head_dim > 128;
+  int rc;
+#define ATT_GO(GC_) (wide ? attn_launch<GC_, true>(cfg, smem, dq, dcache_k, dcache_v, dout, num_heads, num_kv_heads, head_dim, kv_len, msl, scale, nsplit) \
+                          : attn_launch<GC_, false>(cfg, smem, dq, dcache_k, dcache_v, dout, num_heads, num_kv_heads, head_dim, kv_len, msl, scale, nsplit))
+  switch (gc) {
+    case 8: rc = ATT_GO(8); break;
+    case 4: rc = ATT_GO(4); break;
+    case 2: rc = ATT_GO(2); break;
+    default: rc = ATT_GO(1); break;
+  }
+#undef ATT_GO
+  if (rc || nsplit == 1) return rc;
+  cudaLaunchConfig_t mc = {};
+  mc.gridDim = dim3(num_heads); mc.blockDim = dim3((head_dim + 31) & ~31); mc.stream = st;
+  mc.attrs = at; mc.numAttrs = 1;
+  const float* cpart = g_att_part;
+  return cudaLaunchKernelEx(&mc, attn_merge_kernel, cpart, dout, head_dim, nsplit) == cudaSuccess ? WV_OK : WV_ECUDA;
 }
 
 // ------------------------------------------------------------------ SwiGLU gate product and residual add

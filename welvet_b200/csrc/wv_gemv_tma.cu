@@ -43,6 +43,12 @@ struct TmaGeom {
   unsigned red_off;  // float red[2][nrg][nwc][32]
   unsigned gate_off; // gate | up launches: the gate's row sums of this CTA's band (TMA_GATE_ROWS floats)
   unsigned bar_off;  // full[nstage], empty[nstage]
+  // Rows wider than the consumer warps cover (more than 16384 columns) are worked through in ncp column passes
+  // (grouped instance only): cpr and rb[] then describe one pass's slice of a row, pitch[] the whole row, and the
+  // passes' partial row sums wait in shared memory (TMA_GATE_ROWS floats per matrix at part_off).
+  int ncp;
+  unsigned pitch[5];
+  unsigned part_off;
 };
 
 // The matrices one launch works through (same format, columns and group; they share x): the
@@ -138,7 +144,7 @@ __device__ __forceinline__ void load_frag_smem(FragT<F>& f, const LaneOff& a) {
   }
 }
 
-template <int F, int RT, bool PREFETCH, bool EXT>
+template <int F, int RT, bool PREFETCH, bool EXT, bool MP = false>   // MP: column passes (rows wider than 16384 columns)
 __global__ void __launch_bounds__(TMA_THREADS, 1)
 gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* __restrict__ xf, float* __restrict__ y,
                 int row_begin, int row_end, const TmaGeom g, int* __restrict__ err, const typename TmaExtArgs<EXT>::type ext) {
@@ -190,6 +196,7 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
     unsigned ppar = 1;     // parity of the "empty" phase to wait for once the ring has wrapped
     bool wrapped = false;
     int bi = 0;            // matrix being streamed
+    int pcp = 0;           // column pass being streamed
     auto issue_tile = [&](int t) {
       const int s = ps;
       if (wrapped) {
@@ -210,14 +217,71 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
       for (int i = 0; i < 5; i++) {
         const void* pl = src[i];
         if constexpr (EXT) pl = ext.grp.plane[bi][i];
-        if (g.rb[i]) bulk_g2s(dst + g.off[i], (const unsigned char*)pl + (size_t)(row_begin + r0) * g.rb[i], g.rb[i] * nr, full_bar(s));
+        if (!g.rb[i]) continue;
+        bulk_g2s(dst + g.off[i], (const unsigned char*)pl + (size_t)(row_begin + r0) * g.rb[i], g.rb[i] * nr, full_bar(s));
       }
       WV_STAMP_ANY(40 + issued);
       issued++;
       if (++ps == g.nstage) { ps = 0; wrapped = true; ppar ^= 1u; }
     };
+    if constexpr (MP) {
+      // Column passes: a tile is a slice of each of its rows, one copy per row and plane, all issued by lane 0
+      // (spreading the copies over the lanes measured slower: 54 against 40 us at 8192 x 28672).
+      (void)issue_tile; (void)pcp;
+      bool held = false;
+      for (int cpass = 0; cpass < g.ncp && !dead; cpass++)
+      for (bi = 0; bi < nmat && !dead; bi++) {
+        set_band(bi);
+        for (int t = 0; t < ntiles && !dead; t++) {
+          const int s = ps;
+          const int r0 = c_lo + t * g.tr;
+          const int nr = min(g.tr, c_hi - r0);
+          int ok = 1;
+          if (lane == 0) {
+            if (!held && issued >= g.lead) {
+              held = true;
+              for (unsigned i = 0; i < TMA_SPIN_LIMIT; i++) {
+                if (*(volatile unsigned*)&s_xissued >= TMA_CONSUMER_WARPS) break;
+              }
+            }
+            if (wrapped && (*(volatile int*)&s_abort || !mbar_wait(empty_bar(s), ppar))) {
+              if (!*(volatile int*)&s_abort) { atomicCAS_system(err, 0, 100 + s); *(volatile int*)&s_abort = 1; }
+              ok = 0;
+            }
+            if (ok) {
+              unsigned bytes = 0;
+#pragma unroll
+              for (int i = 0; i < 5; i++) bytes += g.rb[i] * nr;
+              mbar_expect_tx(full_bar(s), bytes);
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) { dead = true; break; }
+          const unsigned dst = smem_u32(smem) + (unsigned)s * g.stage_bytes;
+          int id = 0;
+#pragma unroll
+          for (int i = 0; i < 5; i++) {
+            if (!g.rb[i]) continue;
+            const unsigned char* pl = (const unsigned char*)ext.grp.plane[bi][i] + (size_t)(row_begin + r0) * g.pitch[i] + (size_t)cpass * g.rb[i];
+            for (int r = 0; r < nr; r++, id++)
+              if (lane == 0) bulk_g2s(dst + g.off[i] + r * g.rb[i], pl + (size_t)r * g.pitch[i], g.rb[i], full_bar(s));
+          }
+          issued++;
+          if (++ps == g.nstage) { ps = 0; wrapped = true; ppar ^= 1u; }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) {
+        for (int t = max(0, issued - g.nstage); t < issued; t++) {
+          if (!mbar_wait(full_bar(t % g.nstage), (t / g.nstage) & 1)) { atomicCAS_system(err, 0, 200 + t % g.nstage); break; }
+        }
+      }
+      return;
+    }
     if (lane == 0) {
       bool held = false;
+      const int npass = 1;
+      for (pcp = 0; pcp < npass && !dead; pcp++)
       for (bi = 0; bi < nmat && !dead; bi++) {
         set_band(bi);
         for (int t = 0; t < ntiles && !dead; t++) {
@@ -255,10 +319,14 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   // floats gets a 33-float slot so that lanes reading their own chunks element by element
   // hit 32 different banks. Every CTA starts its copy at a different place of x: all SMs
   // asking for the same lines in the same order would queue up at one L2 slice after the other.
-  {
-    const float* xrow = xf + (size_t)blockIdx.y * b.cols;
+  // With column passes, pass cp brings in its own slice of x (after every warp is done with the previous one).
+  const int npass = MP ? g.ncp : 1;
+  int cp = 0;
+  auto copy_x = [&]() {
+    if (cp > 0) asm volatile("bar.sync 15, %0;" ::"n"(TMA_CONSUMER_WARPS * 32) : "memory");
+    const float* xrow = xf + (size_t)blockIdx.y * b.cols + (size_t)cp * g.cpr * 32;
     float* xs = reinterpret_cast<float*>(smem + g.x_off);
-    const int nv = b.cols >> 2;
+    const int nv = g.cpr * 8;
     if ((reinterpret_cast<uintptr_t>(xrow) & 15) == 0) {
       // cols <= 16384: at most 8 vectors per thread; all loads are issued before the first
       // store so that the copy costs one memory round trip, not eight
@@ -281,12 +349,14 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
       }
     } else {
       if (lane == 0) asm volatile("red.relaxed.cta.shared::cta.add.u32 [%0], 1;" ::"r"(smem_u32(&s_xissued)) : "memory");
-      for (int i = tid; i < b.cols; i += TMA_CONSUMER_WARPS * 32) xs[(i >> 5) * 33 + (i & 31)] = __ldg(xrow + i);
+      for (int i = tid; i < g.cpr * 32; i += TMA_CONSUMER_WARPS * 32) xs[(i >> 5) * 33 + (i & 31)] = __ldg(xrow + i);
     }
+    asm volatile("bar.sync 15, %0;" ::"n"(TMA_CONSUMER_WARPS * 32) : "memory");
+  };
+  if (rg >= g.nrg) {   // warps without a row group only help with the copies
+    for (cp = 0; cp < npass; cp++) copy_x();
+    return;
   }
-  asm volatile("bar.sync 15, %0;" ::"n"(TMA_CONSUMER_WARPS * 32) : "memory");
-  WV_STAMP(5);
-  if (rg >= g.nrg) return;
 
   float* red = reinterpret_cast<float*>(smem + g.red_off);
   float* yb = nullptr;
@@ -308,7 +378,12 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
       if (n < nslots && (n / RT) * g.tr + rg * RT + (n % RT) < band && rg * RT + (n % RT) < g.tr) {
         if constexpr (EXT) {
           bool skip = false;
-          if (ext.mode == 1) {
+          if constexpr (MP) {
+            float* sp = reinterpret_cast<float*>(smem + g.part_off) + cur_mat * TMA_GATE_ROWS + (n / RT) * g.tr + rg * RT + (n % RT);
+            if (cp > 0) sum += *sp;
+            if (cp < g.ncp - 1) { *sp = sum; skip = true; }
+          }
+          if (!skip && ext.mode == 1) {
             // SwiGLU gate product (simd/silu.go:14-27) in the epilogue: this thread owns the same row of the
             // gate matrix and of the up matrix, so the gate's sum waits in shared memory for the up row
             float* sg = reinterpret_cast<float*>(smem + g.gate_off);
@@ -456,6 +531,9 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   };
 
   const float* xc = reinterpret_cast<const float*>(smem + g.x_off) + (size_t)(live ? c : 0) * 33;
+  for (cp = 0; cp < npass; cp++) {
+  copy_x();
+  WV_STAMP(5);
   if constexpr (fi.table) {
     // IQ4_NL: f32 grid values from a shared-memory table, activations stay f32
     const unsigned char* tbl = smem + g.red_off + 2u * g.nrg * g.nwc * 32 * 4;
@@ -545,6 +623,7 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
       main_loop([&](const FragT<F>& f) { return idot_chunk<F>(f, xr); });
     }
   }
+  }
   WV_STAMP(4);
   WV_STAMP_NS(7);
 }
@@ -587,8 +666,17 @@ static int launch_tma(const WvDevBlob* bl, int nb, const float* dx, float* const
   constexpr WvFmtInfo fi = wv_fmt_info(F);
   const WvDevBlob& b = bl[0];   // the matrices of a group agree in everything but their row count
   TmaGeom g{};
-  if (!plane_row_bytes(b, g.rb)) return 1;
-  g.cpr = b.cols >> 5;
+  if (!plane_row_bytes(b, g.pitch)) return 1;
+  const int cpr_row = b.cols >> 5;
+  // rows wider than the consumer warps cover go through in column passes of equal width (whole super-blocks)
+  g.ncp = 1;
+  while ((cpr_row + g.ncp - 1) / g.ncp > TMA_CONSUMER_WARPS * 32) g.ncp++;
+  if (g.ncp > 1 && (cpr_row % (g.ncp * 8) || g.ncp > 8)) return 1;
+  g.cpr = cpr_row / g.ncp;
+  for (int i = 0; i < 5; i++) {
+    g.rb[i] = g.pitch[i] / g.ncp;
+    if (g.pitch[i] % g.ncp || g.rb[i] % 16) return 1;
+  }
   g.nwc = (g.cpr + 31) / 32;
   if (g.nwc > TMA_CONSUMER_WARPS) return 1;
   g.nrg = TMA_CONSUMER_WARPS / g.nwc;
@@ -601,7 +689,8 @@ static int launch_tma(const WvDevBlob* bl, int nb, const float* dx, float* const
   const WvFuse* fuse = wv_cur_fuse;
   const bool gated = fuse && fuse->mode == 1;
   const unsigned gate_bytes = gated ? TMA_GATE_ROWS * 4u : 0u;
-  const unsigned fixed = xbytes + align128(2u * g.nrg * g.nwc * 32 * 4 + (fi.table ? 4096u : 0u)) + gate_bytes + 2 * TMA_MAX_STAGES * 8 + 128;
+  const unsigned part_bytes = g.ncp > 1 ? (unsigned)nb * TMA_GATE_ROWS * 4u : 0u;
+  const unsigned fixed = xbytes + align128(2u * g.nrg * g.nwc * 32 * 4 + (fi.table ? 4096u : 0u)) + gate_bytes + part_bytes + 2 * TMA_MAX_STAGES * 8 + 128;
   const unsigned avail = 225u * 1024u;  // 227 KB per CTA minus static shared memory and slack
   if (g.stage_bytes * 2 + fixed > avail) return 1;
   int ns = (int)((avail - fixed) / g.stage_bytes);
@@ -613,7 +702,8 @@ static int launch_tma(const WvDevBlob* bl, int nb, const float* dx, float* const
   g.x_off = g.stage_bytes * ns;
   g.red_off = g.x_off + xbytes;
   g.gate_off = align128(g.red_off + 2u * g.nrg * g.nwc * 32 * 4 + (fi.table ? 4096u : 0u));
-  g.bar_off = g.gate_off + gate_bytes;
+  g.part_off = g.gate_off + gate_bytes;
+  g.bar_off = g.part_off + part_bytes;
   const size_t smem = g.bar_off + 2 * TMA_MAX_STAGES * 8;
 
   int grid = wv_sm_count();
@@ -627,7 +717,12 @@ static int launch_tma(const WvDevBlob* bl, int nb, const float* dx, float* const
     if (nb != 2 || bl[0].rows != bl[1].rows || batch != 1) return WV_ESHAPE;
     if (bl[0].rows / grid + 1 > TMA_GATE_ROWS) return 1;
   }
-  if (nb == 1 && !wv_cur_peers && !fuse) {
+  if (g.ncp > 1) {
+    // the partial sums of a CTA's band wait in shared memory between the passes
+    for (int i = 0; i < nb; i++)
+      if ((nb == 1 ? re - rb_ : bl[i].rows) / grid + 1 > TMA_GATE_ROWS) return 1;
+  }
+  if (nb == 1 && !wv_cur_peers && !fuse && g.ncp == 1) {
     auto kern = gemv_tma_kernel<F, RT, PF, false>;
     static unsigned attr_mask = 0;
     if (!(attr_mask & (1u << dev))) {
@@ -637,11 +732,11 @@ static int launch_tma(const WvDevBlob* bl, int nb, const float* dx, float* const
     e = launch_pdl(kern, dim3(grid, batch), dim3(TMA_THREADS), smem, st, b, xq, dx, dys[0], rb_, re, g, g_err_dev, TmaNoExt{});
   } else {
     if constexpr (RT == 4 && !PF) {   // the grouped / peer-storing variant exists for the default configuration only
-      auto kern = gemv_tma_kernel<F, RT, PF, true>;
-      static unsigned attr_mask = 0;
-      if (!(attr_mask & (1u << dev))) {
+      auto kern = g.ncp > 1 ? gemv_tma_kernel<F, RT, PF, true, true> : gemv_tma_kernel<F, RT, PF, true, false>;
+      static unsigned attr_mask[2] = {0, 0};
+      if (!(attr_mask[g.ncp > 1] & (1u << dev))) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) != cudaSuccess) { wv_set_error("gemv (tma): cannot raise the shared-memory limit"); return WV_ECUDA; }
-        attr_mask |= 1u << dev;
+        attr_mask[g.ncp > 1] |= 1u << dev;
       }
       TmaExt ext{};
       ext.grp.n = nb;

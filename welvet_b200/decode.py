@@ -91,3 +91,97 @@ class BlockDecoder:
         RMSNormCUDA(dh, b["ffn_norm"], b["n2"], 1, c.DModel, c.Eps, stream)
         MatVecSwiGLUCUDA(k["gate"], k["up"], b["n2"], b["ffn"], c.DModel, c.IntermediateDim, stream)
         MatVecAddCUDA(k["down"], b["ffn"], dh, dh, c.IntermediateDim, c.DModel, stream)
+
+
+PROJECTIONS = ("q", "k", "v", "o", "gate", "up", "down")
+
+
+def projection_shapes(cfg: BlockConfig) -> dict:
+    """rows x cols of the seven Dense projections of a block (mha.Config / swiglu.Config)."""
+    qd, kd = cfg.NumHeads * cfg.HeadDim, cfg.NumKVHeads * cfg.HeadDim
+    return {"q": (qd, cfg.DModel), "k": (kd, cfg.DModel), "v": (kd, cfg.DModel), "o": (cfg.DModel, qd),
+            "gate": (cfg.IntermediateDim, cfg.DModel), "up": (cfg.IntermediateDim, cfg.DModel), "down": (cfg.DModel, cfg.IntermediateDim)}
+
+
+def shard_plan(cfg: BlockConfig, rank: int, world: int) -> dict:
+    """Row range [begin, end) of every projection that `rank` of `world` keeps (rows split evenly, as the reference
+    splits rows over goroutines, layers/dense/gemv_parallel.go:24-41)."""
+    return {n: (r * rank // world, r * (rank + 1) // world) for n, (r, _) in projection_shapes(cfg).items()}
+
+
+def vector_layout(cfg: BlockConfig) -> dict:
+    """Float offsets of the gathered vectors inside each rank's exchange buffer: q, k, v, the two hidden-state
+    vectors that alternate between the attention and the FFN half of a block, and the SwiGLU product."""
+    qd, kd = cfg.NumHeads * cfg.HeadDim, cfg.NumKVHeads * cfg.HeadDim
+    off, out = 0, {}
+    for name, n in (("q", qd), ("k", kd), ("v", kd), ("ha", cfg.DModel), ("hb", cfg.DModel), ("ffn", cfg.IntermediateDim)):
+        out[name] = off
+        off += (n + 63) & ~63
+    out["total"] = off
+    return out
+
+
+class ShardedBlockDecoder:
+    """BlockDecoder with every projection row-sharded over `world` ranks: each rank keeps its rows of the seven
+    matrices, its GEMV kernels store their rows into every rank's vectors (peer mappings of one exchange buffer per
+    rank), and arrival flags on the device order the ranks; RMSNorm, RoPE, the cache and attention are replicated.
+    Four sharded launches per block (Q|K|V, O + residual, gate|up with the SiLU product, down + residual), each
+    followed by signal + wait when world > 1.
+
+    The hidden state alternates between the vectors `ha` and `hb` of the exchange buffer: a block reads `ha`, the O
+    projection writes `hb`, the down projection writes `ha` again. A rank can run at most one sharded launch ahead
+    of the slowest rank (it cannot pass a wait before every rank has signalled), and no launch writes a vector that
+    the previous launch's consumers read, so peers never overwrite data still in use.
+
+    keys: this rank's resident shard of q, k, v, o, gate, up, down. local: device pointers of n1, n2, attn and the
+    weights attn_norm / ffn_norm and caches cache_k / cache_v. vec / flags: dense.GatherBuffers."""
+
+    def __init__(self, cfg: BlockConfig, keys: dict, local: dict, rank: int, world: int, vec, flags=None):
+        self.cfg, self.keys, self.local, self.rank, self.world, self.vec, self.flags = cfg, keys, local, rank, world, vec, flags
+        self.off = vector_layout(cfg)
+        plan = shard_plan(cfg, rank, world)
+        self.plan = plan
+
+        def arrays(names, outs):
+            n = len(names)
+            ptrs = []
+            for o in outs:
+                ptrs += [None] * world if o is None else list(vec.pointers(self.off[o]))
+            return ((C.c_uint64 * n)(*[keys[m] for m in names]), (C.c_void_p * (n * world))(*ptrs),
+                    (C.c_int * n)(*[plan[m][0] for m in names]), (C.c_int * n)(*[plan[m][1] - plan[m][0] for m in names]))
+        self._qkv = arrays(("q", "k", "v"), ("q", "k", "v"))
+        self._o = arrays(("o",), ("hb",))
+        self._gu = arrays(("gate", "up"), (None, "ffn"))
+        self._down = arrays(("down",), ("ha",))
+        self._flags_all = (C.c_void_p * world)(*flags.ptrs) if world > 1 else None
+
+    def _sync(self, stream: int) -> None:
+        if self.world > 1:
+            L = lib()
+            check(L.wv_gather_signal(self._flags_all, self.world, self.rank, stream))
+            check(L.wv_gather_wait(self.flags.own, self.world, stream))
+
+    def _gemv(self, a, n: int, dx: int, in_: int, mode: int, dres: Optional[int], stream: int, sync: bool) -> None:
+        check(lib().wv_matvec_dev_group_gather(a[0], n, dx, a[1], self.world, self.rank, a[2], in_, a[3], mode, dres, stream))
+        if sync:
+            self._sync(stream)
+
+    def step(self, pos: int, stream: int = 0, sync: bool = True) -> None:
+        """One token: the hidden state in `ha` of every rank's exchange buffer is updated in place. sync=False leaves
+        the signal / wait kernels out (timing of the launches alone; the ranks then run unordered)."""
+        c, b, own, off = self.cfg, self.local, self.vec.own, self.off
+        qd = c.NumHeads * c.HeadDim
+        ha, hb = own + 4 * off["ha"], own + 4 * off["hb"]
+        q, k, v, ffn = own + 4 * off["q"], own + 4 * off["k"], own + 4 * off["v"], own + 4 * off["ffn"]
+        RMSNormCUDA(ha, b["attn_norm"], b["n1"], 1, c.DModel, c.Eps, stream)
+        self._gemv(self._qkv, 3, b["n1"], c.DModel, 0, None, stream, sync)
+        RoPECacheCUDA(q, k, v, b["cache_k"], b["cache_v"], pos, c.MaxSeqLen, c.NumHeads, c.NumKVHeads, c.HeadDim, c.RoPETheta, stream)
+        AttnDecodeCUDA(q, b["cache_k"], b["cache_v"], b["attn"], c.NumHeads, c.NumKVHeads, c.HeadDim, min(pos + 1, c.MaxSeqLen), c.MaxSeqLen,
+                       1.0 / (c.HeadDim ** 0.5), stream)
+        self._gemv(self._o, 1, b["attn"], qd, 0, ha, stream, sync)
+        RMSNormCUDA(hb, b["ffn_norm"], b["n2"], 1, c.DModel, c.Eps, stream)
+        self._gemv(self._gu, 2, b["n2"], c.DModel, 1, None, stream, sync)
+        self._gemv(self._down, 1, ffn, c.IntermediateDim, 0, hb, stream, sync)
+
+    def launches_per_step(self) -> int:
+        return 8 + (8 if self.world > 1 else 0)
