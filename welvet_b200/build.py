@@ -37,6 +37,7 @@ SOURCES = {
     "wv_gemv_mma.cu": [],
     "wv_decode.cu": [],
     "wv_gemv_tc.cu": [],
+    "wv_gemm_tcgen05.cu": [],
     "wv_api.cu": [],
 }
 

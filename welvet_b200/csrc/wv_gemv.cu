@@ -15,6 +15,7 @@
 //   * warp-shuffle reduction, one store per row.
 #include "wv_gemv_common.cuh"
 #include "wv_dev_hooks.h"
+#include <stdlib.h>
 #include <cstdlib>
 #include <mutex>
 
@@ -644,10 +645,42 @@ static int launch_gemv_regs(const WvDevBlob& b, const float* dx, float* dy, int 
   return WV_EFORMAT;
 }
 
+int wv_launch_gemm_tcgen05(const WvDevBlob& b, const float* dx, float* dy, int batch, int row_begin, int row_end, cudaStream_t st);   // wv_gemm_tcgen05.cu
+// Development switch (libraries built with the hooks only): WV_BATCH_LOOP=1 in the environment keeps batches on the
+// one-row-at-a-time kernels, for timing one path against the other.
+int wv_tma_tuning_rt();   // wv_gemv_tma.cu
+static bool batch_loop_forced() {
+#ifdef WV_DEV_HOOKS
+  static const bool v = [] { const char* e = getenv("WV_BATCH_LOOP"); return e && *e == '1'; }();
+  return v;
+#else
+  return false;
+#endif
+}
+
 int wv_launch_gemv(const WvDevBlob& b, const float* dx, float* dy, int batch, int row_begin, int row_end, cudaStream_t st) {
   if (row_end <= row_begin || batch <= 0) return WV_OK;
   const WvPeers* pp = wv_cur_peers;
   if (pp && batch != 1) return WV_ESHAPE;
+  // Measured at 4096 x 4096 (L2-resident): the tensor-core kernel costs 17-20 us whatever the batch, a batch-1 launch
+  // 5 us per row, so small batches of a matrix that stays in L2 run row by row; a matrix that does not fit L2 would
+  // be streamed from HBM once per row, so there the tensor-core kernel takes every batch.
+  const WvFmtInfo bfi = wv_fmt_info(b.format);
+  const bool big = (double)b.n * (bfi.bits_lo + bfi.bits_hi) / 8.0 > 64e6;
+  if ((batch >= 6 || (batch >= 2 && big)) && !pp && !wv_cur_fuse && !g_tune_r && !wv_tma_tuning_rt() && !batch_loop_forced()) {   // a kernel forced by a tuning code keeps the batch on it
+    // Several activation rows: the tensor-core kernel streams and dequantises the matrix once for up to 256 of
+    // them. What it does not take (FormatNone, ragged rows) runs row by row below.
+    int rc = wv_launch_gemm_tcgen05(b, dx, dy, batch < 256 ? batch : 256, row_begin, row_end, st);
+    if (rc != 1) {
+      for (int b0 = 256; b0 < batch && !rc; b0 += 256) {
+        const int nb = batch - b0 < 256 ? batch - b0 : 256;
+        const float* xs = dx + (size_t)b0 * b.cols;
+        float* ys = dy + (size_t)b0 * b.rows;
+        rc = nb >= 2 ? wv_launch_gemm_tcgen05(b, xs, ys, nb, row_begin, row_end, st) : wv_launch_gemv(b, xs, ys, 1, row_begin, row_end, st);
+      }
+      return rc;
+    }
+  }
   if (b.fast && b.format != WV_NONE && !g_tune_r) {   // an explicit tuning override selects the register-load kernels
     const int rc = wv_launch_gemv_tma(b, dx, dy, batch, row_begin, row_end, st);   // stores to the peers in its epilogue
     if (rc != 1) return rc;

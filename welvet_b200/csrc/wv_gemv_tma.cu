@@ -654,6 +654,7 @@ static int g_tma_rt = 0, g_tma_stages = 0;
 extern "C" void wv_set_tma_tuning(int rows_per_group, int stages) { g_tma_rt = rows_per_group; g_tma_stages = stages; }
 #endif
 int wv_tma_tuning_stages() { return g_tma_stages; }
+int wv_tma_tuning_rt() { return g_tma_rt; }
 static int g_act_width = 0;
 #ifdef WV_DEV_HOOKS
 extern "C" void wv_set_act_width(int limbs) { g_act_width = limbs; }
