@@ -212,6 +212,9 @@ int wv_gather_free(void* dptr);
  * store rows of step k + 1 while a slower rank still reads step k: alternate two sets of output vectors between steps. */
 int wv_gather_signal(unsigned* const* flags_all, int world, int rank, void* stream);
 int wv_gather_wait(unsigned* flags_own, int world, void* stream);
+/* Both in one launch, for a step whose consumers follow immediately: signal as wv_gather_signal does, then wait as
+ * wv_gather_wait does (same counters, same bound on the wait). */
+int wv_gather_sync(unsigned* const* flags_all, int world, int rank, void* stream);
 /* Copy `bytes` from a gather buffer (own or mapped) to host memory after synchronising `stream`. */
 int wv_gather_read(const void* dptr, size_t offset_bytes, void* host, size_t bytes, void* stream);
 

@@ -90,6 +90,39 @@ def test_arrival_flags_in_stream_order_and_timeout(wv):
             f.close()
 
 
+def test_signal_and_wait_in_one_launch(wv):
+    """wv_gather_sync: the signal and the wait of a step as one kernel. Alone on its own flags it passes at once;
+    with a second emulated rank whose signal is already in the stream it passes too, and leaves the same counters
+    as the two separate launches."""
+    L = wv._lib.lib()
+    one = wv.dense.GatherBuffers(4 * 3, 0, 1)
+    try:
+        f1 = (C.c_void_p * 1)(one.own)
+        for step in range(1, 4):
+            wv._lib.check(L.wv_gather_sync(f1, 1, 0, None))
+            torch.cuda.synchronize()
+            assert L.wv_device_status() == 0
+            assert list(one.read(0, 3).view(np.uint32)) == [step, step, step]
+    finally:
+        one.close()
+    world = 2
+    flags = [wv.dense.GatherBuffers(4 * (world + 2), 0, 1) for _ in range(world)]
+    try:
+        f_all = (C.c_void_p * world)(*[f.own for f in flags])
+        for step in range(1, 3):
+            wv._lib.check(L.wv_gather_signal(f_all, world, 1, None))     # rank 1's rows are in
+            wv._lib.check(L.wv_gather_sync(f_all, world, 0, None))       # rank 0 signals and finds both words there
+            wv._lib.check(L.wv_gather_wait(flags[1].own, world, None))
+            torch.cuda.synchronize()
+            assert L.wv_device_status() == 0
+            for r in range(world):
+                assert list(flags[r].read(0, world + 2).view(np.uint32)) == [step] * 4
+        assert L.wv_gather_sync(f_all, 9, 0, None) == wv._lib.WV_EARG
+    finally:
+        for f in flags:
+            f.close()
+
+
 def test_gather_argument_errors(wv):
     L = wv._lib.lib()
     y_all = (C.c_void_p * 1)(0)

@@ -19,7 +19,7 @@ SYMBOLS = [
     "wv_blob_has", "wv_blob_evict", "wv_cache_clear", "wv_cache_bytes", "wv_cache_set_limit",
     "wv_blob_info", "wv_matvec", "wv_matvec_dev", "wv_unpack", "wv_unpack_dev",
     "wv_pack_sizes", "wv_pack", "wv_pack_upload_dev", "wv_device_status", "wv_matvec_dev_static",
-    "wv_argmax_dev", "wv_argmax", "wv_matvec_dev_multi", "wv_matvec_dev_gather", "wv_gather_alloc", "wv_gather_open", "wv_gather_close", "wv_gather_free", "wv_gather_read", "wv_gather_signal", "wv_gather_wait",
+    "wv_argmax_dev", "wv_argmax", "wv_matvec_dev_multi", "wv_matvec_dev_gather", "wv_gather_alloc", "wv_gather_open", "wv_gather_close", "wv_gather_free", "wv_gather_read", "wv_gather_signal", "wv_gather_wait", "wv_gather_sync",
     "wv_matvec_dev_swiglu", "wv_matvec_dev_add", "wv_matvec_dev_group_gather", "wv_rmsnorm_dev", "wv_rope_cache_dev",
     "wv_attn_decode_dev", "wv_silu_mul_dev", "wv_residual_add_dev",
     "wv_topk_sample_dev", "wv_topk_sample", "wv_decode_row", "wv_decode_row_dev",
@@ -88,6 +88,7 @@ def lib() -> C.CDLL:
         L.wv_gather_free.argtypes = [vp]
         L.wv_gather_signal.argtypes = [C.POINTER(vp), i, i, vp]
         L.wv_gather_wait.argtypes = [vp, i, vp]
+        L.wv_gather_sync.argtypes = [C.POINTER(vp), i, i, vp]
         L.wv_gather_read.argtypes = [vp, sz, vp, sz, vp]
         L.wv_matvec_dev_swiglu.argtypes = [u64, u64, vp, vp, i, i, vp]
         L.wv_matvec_dev_add.argtypes = [u64, vp, vp, vp, i, i, vp]

@@ -691,6 +691,14 @@ extern "C" int wv_gather_signal(unsigned* const* flags_all, int world, int rank,
   for (int q = 0; q < world; q++) if (!flags_all[q]) { wv_set_error("wv_gather_signal: flags_all[%d] is null", q); return WV_EARG; }
   return wv_launch_gather_signal(flags_all, world, rank, static_cast<cudaStream_t>(stream));
 }
+int wv_launch_gather_sync(unsigned* const* flags_all, int world, int rank, cudaStream_t st);
+extern "C" int wv_gather_sync(unsigned* const* flags_all, int world, int rank, void* stream) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!flags_all || world < 1 || world > WV_MAX_PEERS || rank < 0 || rank >= world) { wv_set_error("wv_gather_sync: bad argument"); return WV_EARG; }
+  for (int q = 0; q < world; q++) if (!flags_all[q]) { wv_set_error("wv_gather_sync: flags_all[%d] is null", q); return WV_EARG; }
+  return wv_launch_gather_sync(flags_all, world, rank, static_cast<cudaStream_t>(stream));
+}
 extern "C" int wv_gather_wait(unsigned* flags_own, int world, void* stream) {
   int rc = ensure_init();
   if (rc) return rc;

@@ -607,15 +607,30 @@ __global__ void gather_wait_kernel(unsigned* flags, int n, int* err, int max_pol
     if (!ok) atomicCAS_system(err, 0, 700 + (int)threadIdx.x);
   }
 }
-int wv_launch_gather_signal(unsigned* const* flags_all, int world, int rank, cudaStream_t st) {
-  WvFlagPeers p{};
-  p.n = world; p.self = rank;
-  for (int q = 0; q < world; q++) p.f[q] = flags_all[q];
-  gather_signal_kernel<<<1, 32, 0, st>>>(p);
-  return cudaGetLastError() == cudaSuccess ? WV_OK : WV_ECUDA;
+// Signal and wait in one launch (a step whose consumers follow at once needs both, and a launch costs more than
+// either does): thread q tells rank q that this rank's rows are stored, then polls rank q's word here. Launched
+// with programmatic stream serialisation, so that it is resident and past its set-up when the GEMV before it ends.
+__global__ void gather_sync_kernel(const WvFlagPeers p, int* err, int max_polls) {
+  __shared__ unsigned s_sig, s_wait;
+  asm volatile("griddepcontrol.wait;" ::: "memory");              // the preceding kernel's stores are complete and visible
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  unsigned* own = p.f[p.self];
+  if (threadIdx.x == 0) { s_sig = ++own[p.n]; s_wait = ++own[p.n + 1]; }
+  __syncthreads();
+  if ((int)threadIdx.x < p.n) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.f[threadIdx.x] + p.self), "r"(s_sig) : "memory");
+    bool ok = false;
+    for (int i = 0; i < max_polls && !ok; i++) {
+      unsigned v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(own + threadIdx.x) : "memory");
+      ok = (int)(v - s_wait) >= 0;
+      if (!ok) __nanosleep(64);
+    }
+    if (!ok) atomicCAS_system(err, 0, 700 + (int)threadIdx.x);
+  }
 }
-int* wv_tma_err_ptr();
-int wv_launch_gather_wait(unsigned* flags_own, int world, cudaStream_t st) {
+static int gather_max_polls() {
   // Bound of the wait: polls of about a quarter microsecond each. 250 ms by default (host jitter between ranks:
   // a slow graph launch, a first-call attribute set), WELVET_CUDA_GATHER_WAIT_MS overrides it within [1, 2000].
   static int max_polls = 0;
@@ -624,7 +639,30 @@ int wv_launch_gather_wait(unsigned* flags_own, int world, cudaStream_t st) {
     if (const char* e = getenv("WELVET_CUDA_GATHER_WAIT_MS")) { long v = atol(e); if (v >= 1 && v <= 2000) ms = v; }
     max_polls = (int)(ms * 4000);
   }
-  gather_wait_kernel<<<1, 32, 0, st>>>(flags_own, world, wv_tma_err_ptr(), max_polls);
+  return max_polls;
+}
+int* wv_tma_err_ptr();
+int wv_launch_gather_sync(unsigned* const* flags_all, int world, int rank, cudaStream_t st) {
+  WvFlagPeers p{};
+  p.n = world; p.self = rank;
+  for (int q = 0; q < world; q++) p.f[q] = flags_all[q];
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1); cfg.blockDim = dim3(32); cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, gather_sync_kernel, p, wv_tma_err_ptr(), gather_max_polls()) == cudaSuccess ? WV_OK : WV_ECUDA;
+}
+int wv_launch_gather_signal(unsigned* const* flags_all, int world, int rank, cudaStream_t st) {
+  WvFlagPeers p{};
+  p.n = world; p.self = rank;
+  for (int q = 0; q < world; q++) p.f[q] = flags_all[q];
+  gather_signal_kernel<<<1, 32, 0, st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? WV_OK : WV_ECUDA;
+}
+int wv_launch_gather_wait(unsigned* flags_own, int world, cudaStream_t st) {
+  gather_wait_kernel<<<1, 32, 0, st>>>(flags_own, world, wv_tma_err_ptr(), gather_max_polls());
   return cudaGetLastError() == cudaSuccess ? WV_OK : WV_ECUDA;
 }
 

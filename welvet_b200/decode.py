@@ -66,8 +66,8 @@ class BlockConfig:
 
 
 class BlockDecoder:
-    """One block's single-token decode as eight launches: RMSNorm, Q|K|V group, RoPE + cache write,
-    attention, O + residual, RMSNorm, gate|up with the SiLU product, down + residual. `keys` maps
+    """One block's single-token decode as nine launches: RMSNorm, Q|K|V group, RoPE + cache write,
+    attention (splits, then their merge), O + residual, RMSNorm, gate|up with the SiLU product, down + residual. `keys` maps
     q, k, v, o, gate, up, down to resident blob keys; `bufs` maps the working vectors (n1, q, k, v,
     attn, n2, ffn) and the weights attn_norm / ffn_norm and caches cache_k / cache_v to device pointers."""
 
@@ -126,7 +126,7 @@ class ShardedBlockDecoder:
     matrices, its GEMV kernels store their rows into every rank's vectors (peer mappings of one exchange buffer per
     rank), and arrival flags on the device order the ranks; RMSNorm, RoPE, the cache and attention are replicated.
     Four sharded launches per block (Q|K|V, O + residual, gate|up with the SiLU product, down + residual), each
-    followed by signal + wait when world > 1.
+    followed by the signal-and-wait launch when world > 1.
 
     The hidden state alternates between the vectors `ha` and `hb` of the exchange buffer: a block reads `ha`, the O
     projection writes `hb`, the down projection writes `ha` again. A rank can run at most one sharded launch ahead
@@ -158,8 +158,7 @@ class ShardedBlockDecoder:
     def _sync(self, stream: int) -> None:
         if self.world > 1:
             L = lib()
-            check(L.wv_gather_signal(self._flags_all, self.world, self.rank, stream))
-            check(L.wv_gather_wait(self.flags.own, self.world, stream))
+            check(L.wv_gather_sync(self._flags_all, self.world, self.rank, stream))
 
     def _gemv(self, a, n: int, dx: int, in_: int, mode: int, dres: Optional[int], stream: int, sync: bool) -> None:
         check(lib().wv_matvec_dev_group_gather(a[0], n, dx, a[1], self.world, self.rank, a[2], in_, a[3], mode, dres, stream))
@@ -184,4 +183,4 @@ class ShardedBlockDecoder:
         self._gemv(self._down, 1, ffn, c.IntermediateDim, 0, hb, stream, sync)
 
     def launches_per_step(self) -> int:
-        return 8 + (8 if self.world > 1 else 0)
+        return 9 + (4 if self.world > 1 else 0)
