@@ -166,16 +166,6 @@ def run_reference(args, rank, world):
            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": desc},
            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
            "gpu_launches": 0}
-    if world == 1 and not args.quick and not args.formats and not args.no_decode:
-        for j in jobs + extra_jobs:
-            L.wv_blob_evict(j["key"])
-        decode = run_decode_configs(torch, L, _lib, stream, 0, 1, None, None)
-        O3 = None
-        if not args.no_parity:
-            import oracle as O3
-        decode["config3"] = small_batch_gemm(torch, L, _lib, stream, O3)
-    if not args.quick and not args.formats and not args.no_decode:
-        out.update(decode)
     emit(out)
 
 
@@ -549,6 +539,45 @@ def small_batch_gemm(torch, L, _lib, stream, O):
     return out
 
 
+def size_sweep(torch, L, _lib, stream):
+    """Launch time against matrix size for three formats (same timing method as the per-format table): the least-squares
+    line t = fixed + bytes / rate separates the per-launch overhead from the streaming rate."""
+    shapes = [(2368, 14336), (4096, 14336), (8192, 8192), (14336, 8192), (28672, 8192), (65536, 8192)]
+    out = {}
+    key = 0x600000
+    for name, fmt in (("Q4_0", 2), ("Q4_K", 8), ("Q8_0", 1)):
+        pts = []
+        for rows, cols in shapes:
+            w = torch.randn(rows * cols, device="cuda") * 0.02
+            x = torch.randn(cols, device="cuda")
+            y = torch.zeros(rows, device="cuda")
+            keys, nbytes = [], 0
+            for k in range(32):
+                key += 1
+                _lib.check(L.wv_pack_upload_dev(key, fmt, 1, 0, w.data_ptr(), rows, cols, None))
+                wb = C.c_uint64()
+                _lib.check(L.wv_blob_info(key, None, None, C.byref(wb), None, None))
+                nbytes = int(wb.value)
+                keys.append(key)
+                if len(keys) * nbytes >= 300e6 and len(keys) >= 2:
+                    break
+            K, n_l = len(keys), 4 * len(keys)
+
+            def run(st):
+                for i in range(n_l):
+                    _lib.check(L.wv_matvec_dev(keys[i % K], x.data_ptr(), y.data_ptr(), 1, cols, rows, st))
+            us = _timed_graph(torch, stream, None, run) / n_l * 1e3
+            pts.append({"rows": rows, "cols": cols, "packed_bytes": nbytes, "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1)})
+            for k in keys:
+                L.wv_blob_evict(k)
+            del w
+        b = np.array([p["packed_bytes"] for p in pts], np.float64)
+        t = np.array([p["us"] for p in pts], np.float64)
+        slope, fixed = np.polyfit(b, t, 1)
+        out[name] = {"points": pts, "fixed_us": round(float(fixed), 2), "streaming_gbs": round(1e-3 / float(slope), 1)}
+    return out
+
+
 def run_decode_configs(torch, L, _lib, stream, rank, world, exchange, dist):
     """The decode configurations beside the headline sweep: the 8B stack on one GPU (tokens/s, one block checked against
     the reference's host arithmetic) and the 70B stack with its LM head as Q8_0 and Q4_K, row-sharded over the ranks."""
@@ -599,6 +628,7 @@ def main():
     ap.add_argument("--impl", default="welvet_b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the per-format parity fields")
+    ap.add_argument("--size-sweep", action="store_true", help="only: launch time against matrix size for Q4_0 / Q4_K / Q8_0 (prints its own JSON line)")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-stack decode runs (8B block stack, 70B row-sharded stack and LM head)")
     ap.add_argument("--formats", default="", help="comma list: restrict the sweep (for profiler captures)")
     ap.add_argument("--quick", action="store_true", help="skip the per-format table, the e2e and the CPU legs (profiler captures)")
@@ -611,6 +641,8 @@ def main():
         return
     args.warmup = max(args.warmup, 3)
     sweep = [f for f in SWEEP if not args.formats or f[0] in args.formats.split(",")]
+    if args.formats:       # a restricted run (profiler captures) may also name the formats measured outside the step
+        sweep += [f for f in EXTRA if f[0] in args.formats.split(",")]
     extra = [] if (args.formats or args.quick) else EXTRA
 
     import torch
@@ -623,6 +655,10 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     stream = torch.cuda.Stream()
+    if args.size_sweep:
+        if rank == 0:
+            emit({"size_sweep": size_sweep(torch, L, _lib, stream), "unit": "us per launch; GB/s of packed weight bytes", "n_gpus": 1})
+        return
 
     # ---- build the sweep on the device (device packer == reference packer, byte for byte)
     jobs = []
@@ -842,19 +878,36 @@ def main():
     # ---- end to end through the host-pointer plugin call
     yh = {j["key"]: np.zeros(j["r1"] - j["r0"], np.float32) for j in jobs}
 
-    def e2e_step():
-        for j in jobs:
-            _lib.check(L.wv_matvec(j["key"], xh[j["cols"]].ctypes.data, yh[j["key"]].ctypes.data, 1, j["cols"], j["r1"] - j["r0"]))
-    e2e_val = None
+    def e2e_call(j):
+        _lib.check(L.wv_matvec(j["key"], xh[j["cols"]].ctypes.data, yh[j["key"]].ctypes.data, 1, j["cols"], j["r1"] - j["r0"]))
+
+    def e2e_step(pool):
+        if pool is None:
+            for j in jobs:
+                e2e_call(j)
+        else:
+            list(pool.map(e2e_call, jobs))
+    e2e_val, e2e_single = None, None
+    E2E_CALLERS = 4
     if world == 1 and not args.quick:
-        for _ in range(3):
-            e2e_step()
+        # Every call is the synchronous host-pointer plugin call (x copied in, y copied out inside it). The headline figure
+        # has four caller threads in flight, as the reference's Dense is called from several goroutines
+        # (layers/dense/cpu.go forwardTiledMC) and as the library's four staging slots allow; one caller is reported beside it.
+        from concurrent.futures import ThreadPoolExecutor
         n_e2e = max(args.steps, 20)
-        t0 = time.perf_counter()
-        for _ in range(n_e2e):
-            e2e_step()
-        e2e_s = (time.perf_counter() - t0) / n_e2e
-        e2e_val = full_bytes / e2e_s / 1e9
+        for callers in (1, E2E_CALLERS):
+            pool = ThreadPoolExecutor(callers) if callers > 1 else None
+            for _ in range(3):
+                e2e_step(pool)
+            t0 = time.perf_counter()
+            for _ in range(n_e2e):
+                e2e_step(pool)
+            e2e_s = (time.perf_counter() - t0) / n_e2e
+            if pool is not None:
+                pool.shutdown()
+                e2e_val = full_bytes / e2e_s / 1e9
+            else:
+                e2e_single = full_bytes / e2e_s / 1e9
 
     cfg = common_config(sweep)
     out = {
@@ -889,7 +942,7 @@ def main():
                              "max_rel_worst": max(p.get("max_rel", 0.0) for p in per), "tolerance": 1e-3,
                              "rows_checked": "three 64-row bands (first, middle, last) of every matrix"}
     if e2e_val is not None:
-        out["e2e"] = {"value": e2e_val, "unit": "GB/s",
+        out["e2e"] = {"value": e2e_val, "unit": "GB/s", "callers": E2E_CALLERS, "value_one_caller": e2e_single,
                       "h2d_bytes_per_step": int(sum(4 * j["cols"] for j in jobs)),
                       "d2h_bytes_per_step": int(sum(4 * (j["r1"] - j["r0"]) for j in jobs))}
     if world == 1 and not args.no_cpu_baseline and not args.quick:
@@ -901,6 +954,10 @@ def main():
         for j in jobs + extra_jobs:
             L.wv_blob_evict(j["key"])
         decode = run_decode_configs(torch, L, _lib, stream, 0, 1, None, None)
+        O3 = None
+        if not args.no_parity:
+            import oracle as O3
+        decode["config3"] = small_batch_gemm(torch, L, _lib, stream, O3)
     if not args.quick and not args.formats and not args.no_decode:
         out.update(decode)
     emit(out)

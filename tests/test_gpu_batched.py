@@ -107,3 +107,40 @@ def test_dense_forward_batched(wv):
         assert np.all(np.abs(pre[m] - ref) <= TOL * den + 1e-6)
         pm = pre[m].astype(np.float64)
         assert np.allclose(post[m], pm / (1 + np.exp(-pm)), rtol=1e-5, atol=1e-6)
+
+
+def test_host_pointer_calls_from_threads(wv):
+    """wv_matvec (host pointers in and out) from six threads at once, as goroutines call Dense in the reference: the
+    staging slots keep the calls apart, every result equals the single-threaded one bit for bit."""
+    import threading
+    q = wv.quant
+    rng = np.random.default_rng(31)
+    jobs = []
+    for i, (fmt, rows, cols) in enumerate((("Q4_K", 512, 4096), ("Q8_0", 300, 2048), ("IQ3_S", 1000, 1024), ("Q4_0", 96, 14336),
+                                           ("Q6_K", 700, 2048), ("BinaryPacked", 256, 4096))):
+        w = rng.normal(0, 0.02, rows * cols).astype(np.float32)
+        blob = q.Pack(q.Format["Format" + fmt], w, rows, cols)
+        x = rng.normal(0, 1, cols).astype(np.float32)
+        want = np.zeros(rows, np.float32)
+        q.MatVec(blob, x, want)
+        jobs.append((blob, x, want))
+    errors = []
+
+    def worker(job):
+        blob, x, want = job
+        try:
+            for _ in range(50):
+                y = np.full(blob.Rows, np.nan, np.float32)
+                q.MatVec(blob, x, y)
+                if not np.array_equal(y.view(np.uint32), want.view(np.uint32)):
+                    errors.append("mismatch")
+                    return
+        except Exception as e:   # noqa: BLE001
+            errors.append(repr(e))
+    threads = [threading.Thread(target=worker, args=(j,)) for j in jobs]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors[:3]
+    assert wv._lib.lib().wv_device_status() == 0

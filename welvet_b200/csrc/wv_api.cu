@@ -9,6 +9,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 #include <unordered_map>
 #include <vector>
@@ -39,13 +40,10 @@ struct Entry {
   size_t dev_bytes = 0, wire_bytes = 0;
 };
 static std::mutex g_mu;                // guards the map and the byte counters
-static std::mutex g_stage_mu;          // guards the host staging buffers of wv_matvec / wv_unpack
 static std::unordered_map<uint64_t, Entry> g_cache;
 static uint64_t g_cache_bytes = 0, g_cache_limit = 0;
 static int g_device = -1;
 static cudaStream_t g_stream = nullptr;
-static float *g_hx = nullptr, *g_hy = nullptr, *g_dx = nullptr, *g_hy_dev = nullptr;
-static size_t g_hx_n = 0, g_hy_n = 0, g_dx_n = 0;
 
 extern "C" int wv_device_count(void) {
   int n = 0;
@@ -761,6 +759,40 @@ static int grow(float** p, size_t* cap, size_t n, bool pinned) {
   return WV_OK;
 }
 
+// ---------------------------------------------------------------- host-pointer call
+// A small pool of staging slots, each with its own stream: concurrent callers (the reference calls Dense from several
+// goroutines, layers/dense/cpu.go forwardTiledMC) overlap instead of queueing on one lock. x is copied into mapped pinned
+// memory and brought to the device by a one-CTA kernel (a copy-engine transfer of a few kilobytes costs more in start-up
+// than in transfer); the GEMV behind it is launched with programmatic stream serialisation, so its prologue overlaps
+// that kernel; y is stored by the GEMV straight into mapped pinned memory. Calls with a batch share slot 0: the
+// batched kernel's split scratch belongs to the library and takes one launch at a time.
+struct StageSlot {
+  std::mutex mu;
+  cudaStream_t st = nullptr;
+  float *hx = nullptr, *hx_dev = nullptr, *dx = nullptr, *hy = nullptr, *hy_dev = nullptr;
+  size_t hx_n = 0, dx_n = 0, hy_n = 0;
+};
+#define WV_STAGE_SLOTS 4
+static StageSlot g_slots[WV_STAGE_SLOTS];
+static std::atomic<unsigned> g_slot_rr{0};
+
+__global__ void __launch_bounds__(256) stage_in_kernel(const float4* __restrict__ src, float4* __restrict__ dst, int n4, const float* __restrict__ src1,
+                                                       float* __restrict__ dst1, int tail) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) dst[i] = src[i];
+  if (blockIdx.x == 0 && (int)threadIdx.x < tail) dst1[threadIdx.x] = src1[threadIdx.x];
+}
+
+static int grow_mapped(float** h, float** d, size_t* cap, size_t n) {
+  if (*cap >= n) return WV_OK;
+  if (*h) { cudaFreeHost(*h); *h = nullptr; *cap = 0; }
+  const size_t want = n + n / 2 + 1024;
+  if (cudaHostAlloc(h, want * 4, cudaHostAllocMapped) != cudaSuccess) { cudaGetLastError(); wv_set_error("staging allocation of %zu floats failed", want); return WV_ENOMEM; }
+  if (cudaHostGetDevicePointer(d, *h, 0) != cudaSuccess) { cudaGetLastError(); cudaFreeHost(*h); *h = nullptr; wv_set_error("no device alias for a staging buffer"); return WV_ECUDA; }
+  *cap = want;
+  return WV_OK;
+}
+
 extern "C" int wv_matvec(uint64_t key, const float* x, float* y, int batch, int in, int out) {
   int rc = ensure_init();
   if (rc) return rc;
@@ -769,24 +801,40 @@ extern "C" int wv_matvec(uint64_t key, const float* x, float* y, int batch, int 
   if ((rc = lookup(key, &e))) return rc;
   if ((rc = check_dims(e, batch, in, out))) return rc;
   const size_t nx = (size_t)batch * in, ny = (size_t)batch * out;
-  std::lock_guard<std::mutex> lk(g_stage_mu);
-  if ((rc = grow(&g_hx, &g_hx_n, nx, true)) || (rc = grow(&g_dx, &g_dx_n, nx, false))) return rc;
-  // y lives in mapped pinned host memory: the kernels write each output once with plain stores, so
-  // they store straight to the host and the call needs no device-to-host copy
-  if (g_hy_n < ny) {
-    if (g_hy) { cudaFreeHost(g_hy); g_hy = nullptr; g_hy_n = 0; }
-    const size_t want = ny + ny / 2 + 1024;
-    if (cudaHostAlloc(&g_hy, want * 4, cudaHostAllocMapped) != cudaSuccess) { cudaGetLastError(); wv_set_error("staging allocation of %zu floats failed", want); return WV_ENOMEM; }
-    if (cudaHostGetDevicePointer(&g_hy_dev, g_hy, 0) != cudaSuccess) { cudaGetLastError(); cudaFreeHost(g_hy); g_hy = nullptr; wv_set_error("no device alias for the output staging buffer"); return WV_ECUDA; }
-    g_hy_n = want;
+  StageSlot* slot = nullptr;
+  if (batch == 1) {
+    const unsigned first = g_slot_rr.fetch_add(1);
+    for (unsigned i = 0; i < WV_STAGE_SLOTS && !slot; i++) {
+      StageSlot& c = g_slots[(first + i) % WV_STAGE_SLOTS];
+      if (c.mu.try_lock()) slot = &c;
+    }
+    if (!slot) { slot = &g_slots[first % WV_STAGE_SLOTS]; slot->mu.lock(); }
+  } else {
+    slot = &g_slots[0];
+    slot->mu.lock();
   }
-  memcpy(g_hx, x, nx * 4);
-  CUDA_TRY(cudaMemcpyAsync(g_dx, g_hx, nx * 4, cudaMemcpyHostToDevice, g_stream));
-  rc = wv_launch_gemv(e.blob, g_dx, g_hy_dev, batch, 0, e.blob.rows, g_stream);
+  std::lock_guard<std::mutex> lk(slot->mu, std::adopt_lock);
+  if (!slot->st) {
+    if (slot == &g_slots[0]) slot->st = g_stream;
+    else CUDA_TRY(cudaStreamCreateWithFlags(&slot->st, cudaStreamNonBlocking));
+  }
+  if ((rc = grow_mapped(&slot->hx, &slot->hx_dev, &slot->hx_n, nx)) || (rc = grow(&slot->dx, &slot->dx_n, nx, false)) ||
+      (rc = grow_mapped(&slot->hy, &slot->hy_dev, &slot->hy_n, ny))) return rc;
+  memcpy(slot->hx, x, nx * 4);
+  {
+    const int n4 = (int)(nx / 4), tail = (int)(nx % 4);
+    int blocks = (n4 + 255) / 256;
+    if (blocks > 16) blocks = 16;
+    if (blocks < 1) blocks = 1;
+    stage_in_kernel<<<blocks, 256, 0, slot->st>>>(reinterpret_cast<const float4*>(slot->hx_dev), reinterpret_cast<float4*>(slot->dx), n4,
+                                                 slot->hx_dev + (size_t)n4 * 4, slot->dx + (size_t)n4 * 4, tail);
+    CUDA_TRY(cudaGetLastError());
+  }
+  rc = wv_launch_gemv(e.blob, slot->dx, slot->hy_dev, batch, 0, e.blob.rows, slot->st);
   if (rc) { wv_set_error("wv_matvec: launch failed (%d): %s", rc, cudaGetErrorString(cudaGetLastError())); return rc; }
-  CUDA_TRY(cudaStreamSynchronize(g_stream));
+  CUDA_TRY(cudaStreamSynchronize(slot->st));
   if (int te = wv_tma_take_error()) { wv_set_error("wv_matvec: a bounded device wait ran out (code %d)", te); return WV_ETIMEOUT; }
-  memcpy(y, g_hy, ny * 4);
+  memcpy(y, slot->hy, ny * 4);
   return WV_OK;
 }
 
