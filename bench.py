@@ -240,9 +240,9 @@ def _pack_rows(torch, L, _lib, key, fmt, rows, cols, r0, r1, gen):
 
 class DecodeStack:
     """A whole Llama-shaped stack for single-token decode on the device, every projection in the 4-bit k-quant and
-    row-sharded over `world` ranks. Per token: embedding row, then per block RMSNorm, Q|K|V, RoPE + cache write,
-    attention over 2049 positions, O + residual, RMSNorm, gate|up with the SiLU product, down + residual; then the
-    final RMSNorm, the LM head and the greedy pick. All blocks have their own weights and caches."""
+    row-sharded over `world` ranks. Per token: embedding row, then per block Q|K|V (RMSNorm in its prologue), RoPE +
+    cache write, attention over 2049 positions, O + residual, gate|up (RMSNorm in its prologue, SiLU product in its
+    epilogue), down + residual; then the LM head (final RMSNorm in its prologue) and the greedy pick. All blocks have their own weights and caches."""
 
     def __init__(self, torch, L, _lib, name, head_formats, rank, world, exchange, layers=None, full_rows=False):
         from welvet_b200.decode import BlockConfig, ShardedBlockDecoder, projection_shapes, shard_plan, vector_layout
@@ -265,7 +265,7 @@ class DecodeStack:
         self.logits_off = lay["total"]
         self.vec = GatherBuffers(4 * (lay["total"] + ((vocab + 63) & ~63)), rank, world, exchange)
         self.flags = GatherBuffers(4 * (world + 2), rank, world, exchange) if world > 1 else None
-        self.local = {n: torch.zeros(sz, device="cuda") for n, sz in (("n1", d), ("n2", d), ("attn", cfg.NumHeads * cfg.HeadDim))}
+        self.local = {"attn": torch.zeros(cfg.NumHeads * cfg.HeadDim, device="cuda")}
         self.gamma = torch.ones(d, device="cuda")
         self.decs, self.keys, self.caches, self.bytes_rank = [], [], [], 0
         # the token's embedding row: a small f32 matrix whose row 0 is fetched by the DecodeRow entry
@@ -311,15 +311,16 @@ class DecodeStack:
             dec.step(CTX, st, flags)
         if head is None:
             return
-        chk(L.wv_rmsnorm_dev(ha, self.gamma.data_ptr(), self.local["n1"].data_ptr(), 1, d, cfg.Eps, st))
-        chk(L.wv_matvec_dev_gather(self.heads[head][0], self.local["n1"].data_ptr(), self.logits_all, self.sworld, self.srank, self.h0,
-                                   d, self.h1 - self.h0, st))
+        from welvet_b200.decode import MatVecFusedCUDA        # final RMSNorm in the LM head's prologue
+        MatVecFusedCUDA((C.c_uint64 * 1)(self.heads[head][0]), ha, self.logits_all, d, (C.c_int * 1)(self.h1 - self.h0),
+                        dnorm_gamma=self.gamma.data_ptr(), norm_eps=cfg.Eps, world=self.sworld, rank=self.srank,
+                        row_offset=(C.c_int * 1)(self.h0), stream=st)
         if flags:
             self.sync(st)
         chk(L.wv_argmax_dev(self.vec.own + 4 * self.logits_off, self.m["vocab"], self.pick.data_ptr(), st))
 
     def launches_per_token(self):
-        return 1 + self.layers * self.decs[0].launches_per_step() + (4 if self.sworld > 1 else 3)
+        return 1 + self.layers * self.decs[0].launches_per_step() + (3 if self.sworld > 1 else 2)
 
     def hidden(self):
         return self.vec.read(self.lay["ha"], self.cfg.DModel)
@@ -628,6 +629,7 @@ def main():
     ap.add_argument("--impl", default="welvet_b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the per-format parity fields")
+    ap.add_argument("--e2e-callers", type=int, default=8, help="caller threads of the end-to-end measurement (the library has eight staging slots)")
     ap.add_argument("--size-sweep", action="store_true", help="only: launch time against matrix size for Q4_0 / Q4_K / Q8_0 (prints its own JSON line)")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-stack decode runs (8B block stack, 70B row-sharded stack and LM head)")
     ap.add_argument("--formats", default="", help="comma list: restrict the sweep (for profiler captures)")
@@ -888,11 +890,11 @@ def main():
         else:
             list(pool.map(e2e_call, jobs))
     e2e_val, e2e_single = None, None
-    E2E_CALLERS = 4
+    E2E_CALLERS = args.e2e_callers
     if world == 1 and not args.quick:
         # Every call is the synchronous host-pointer plugin call (x copied in, y copied out inside it). The headline figure
-        # has four caller threads in flight, as the reference's Dense is called from several goroutines
-        # (layers/dense/cpu.go forwardTiledMC) and as the library's four staging slots allow; one caller is reported beside it.
+        # has several caller threads in flight (eight by default), as the reference's Dense is called from several goroutines
+        # (layers/dense/cpu.go forwardTiledMC) and as the library's eight staging slots allow; one caller is reported beside it.
         from concurrent.futures import ThreadPoolExecutor
         n_e2e = max(args.steps, 20)
         for callers in (1, E2E_CALLERS):

@@ -195,6 +195,23 @@ int wv_matvec_dev_gather(uint64_t key, const float* dx, float* const* y_all, int
  * wv_matvec_dev_gather. */
 int wv_matvec_dev_group_gather(const uint64_t* keys, int n, const float* dx, float* const* y_all, int world, int rank,
                                const int* row_offset, int in, const int* out_local, int mode, const float* dresidual, void* stream);
+/* Everything the grouped launch can fuse, in one descriptor (the entries above are special cases of it): n <= 4
+ * matrices of one format and column count on a shared x; optionally x is RMS-normalised on its way in
+ * (dnorm_gamma non-NULL: x_j / sqrt(mean(x^2) + norm_eps) * gamma_j in float64, layers/rmsnorm/cpu.go:32-90 — the norm's
+ * own launch and its output vector disappear); mode 1 applies the SwiGLU gate product (swiglu/cpu.go:29-52); dresidual adds
+ * a residual (model/transformer/forward.go:65,75); world > 1 stores every row into all ranks' vectors. The reference
+ * fuses the same steps in its WGSL shaders (fusedgpu/shaders.go:59-222, hybrid_shaders.go:82). Fields as in
+ * wv_matvec_dev_group_gather; with world == 1 y_all holds the n local vectors and row_offset may be NULL. */
+typedef struct WvFusedCall {
+  const uint64_t* keys; int n;
+  const float* dx;
+  float* const* y_all; int world, rank;
+  const int* row_offset; int in; const int* out_local;
+  int mode;
+  const float* dresidual;
+  const float* dnorm_gamma; double norm_eps;
+} WvFusedCall;
+int wv_matvec_dev_fused(const WvFusedCall* call, void* stream);
 /* Plumbing for the vectors above (cudaMalloc + cudaIpcGetMemHandle / cudaIpcOpenMemHandle with lazy peer
  * access): allocate an exportable device buffer and its 64-byte handle; map a peer's handle; unmap; free. */
 int wv_gather_alloc(size_t bytes, void** dptr, unsigned char handle[64]);

@@ -136,6 +136,66 @@ def test_fused_swiglu_and_residual_epilogues(wv, fmt, shape):
             L.wv_blob_evict(k)
 
 
+@pytest.mark.parametrize("fmt", ["Q4_K", "Q8_0", "IQ4_NL", "none"])
+@pytest.mark.parametrize("cols", [4096, 8192, 1000])
+def test_rmsnorm_in_the_prologue_of_the_grouped_launch(wv, fmt, cols):
+    """Q|K|V on RMSNorm(x) as one launch (the norm in the GEMV's prologue) against the norm's own launch followed by the
+    grouped launch, and against the oracle's float64 norm and SIMD-path GEMVs; then gate|up with the SiLU product."""
+    import ctypes as C
+    import torch
+    from welvet_b200 import _lib
+    from welvet_b200.decode import MatVecFusedCUDA, RMSNormCUDA
+    L = _lib.lib()
+    shapes = [(640, cols), (128, cols), (128, cols)]
+    obs, keys = [], []
+    for i, (r, c) in enumerate(shapes):
+        w = make_w(50 + i, r, c)[0]
+        ob = O.pack(fmt, w, r, c)
+        k = 0x3E0000 + i
+        _lib.check(L.wv_blob_upload(k, ob.format, 1, r, c, ob.block_weights, ob.raw.ctypes.data, ob.raw.size,
+                                    ob.scales.ctypes.data if ob.scales.size else None, ob.scales.size,
+                                    ob.mins.ctypes.data if ob.mins.size else None, ob.mins.size))
+        obs.append(ob); keys.append(k)
+    try:
+        rng = np.random.default_rng(cols)
+        x = (rng.normal(0, 3, cols)).astype(np.float32)
+        gamma = rng.normal(1, 0.1, cols).astype(np.float32)
+        dx, dg = _dev(x), _dev(gamma)
+        ys = [torch.full((r,), float("nan"), device="cuda") for r, _ in shapes]
+        ka = (C.c_uint64 * 3)(*keys)
+        outs = (C.c_int * 3)(*[r for r, _ in shapes])
+        MatVecFusedCUDA(ka, dx.data_ptr(), (C.c_void_p * 3)(*[y.data_ptr() for y in ys]), cols, outs, dnorm_gamma=dg.data_ptr(), norm_eps=1e-5)
+        xn = torch.zeros(cols, device="cuda")
+        RMSNormCUDA(dx.data_ptr(), dg.data_ptr(), xn.data_ptr(), 1, cols, 1e-5)
+        refs = [torch.zeros(r, device="cuda") for r, _ in shapes]
+        _lib.check(L.wv_matvec_dev_multi(ka, 3, xn.data_ptr(), (C.c_void_p * 3)(*[y.data_ptr() for y in refs]), 1, cols, outs, None))
+        torch.cuda.synchronize()
+        assert L.wv_device_status() == 0
+        xn_ref = O.rmsnorm(x, gamma)
+        assert np.max(np.abs(xn.cpu().numpy() - xn_ref)) <= 1e-6 * np.max(np.abs(xn_ref))
+        for ob, y, ref in zip(obs, ys, refs):
+            want = O.matvec_simd(ob, xn_ref, 0)
+            den = O.sum_abs_wx(ob, xn_ref)
+            got = y.cpu().numpy().astype(np.float64)
+            assert np.all(np.abs(got - want) <= TOL * den + 1e-30)
+            # the two device routes differ at most by the rounding of 1 / rms in its last float64 bits
+            assert np.all(np.abs(got - ref.cpu().numpy()) <= 2e-6 * den + 1e-30)
+        if fmt != "none":
+            h = torch.full((shapes[1][0],), float("nan"), device="cuda")
+            k2 = (C.c_uint64 * 2)(keys[1], keys[2])
+            MatVecFusedCUDA(k2, dx.data_ptr(), (C.c_void_p * 2)(None, h.data_ptr()), cols, (C.c_int * 2)(128, 128), mode=1,
+                            dnorm_gamma=dg.data_ptr(), norm_eps=1e-5)
+            torch.cuda.synchronize()
+            g_ref, u_ref = (O.matvec_simd(ob, xn_ref, 0) for ob in obs[1:])
+            want = O.silu_mul(g_ref, u_ref).astype(np.float64)
+            dg_, du_ = (TOL * O.sum_abs_wx(ob, xn_ref) for ob in obs[1:])
+            bound = 1.1 * dg_ * np.abs(u_ref) + np.abs(g_ref) * du_ + dg_ * du_ + 1e-6 * np.abs(want) + 1e-30
+            assert np.all(np.abs(h.cpu().numpy().astype(np.float64) - want) <= bound)
+    finally:
+        for k in keys:
+            L.wv_blob_evict(k)
+
+
 def test_decoder_block_decode_on_device(wv):
     """The 8B block of the decoder configuration (d_model 4096, 32 / 8 heads of 128, FFN 14336, Q4_K, KV cache of
     2048 positions, RMSNorm eps 1e-5, RoPE theta 10000) decoded for one token entirely on the device, against the

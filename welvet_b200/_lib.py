@@ -20,7 +20,7 @@ SYMBOLS = [
     "wv_blob_info", "wv_matvec", "wv_matvec_dev", "wv_unpack", "wv_unpack_dev",
     "wv_pack_sizes", "wv_pack", "wv_pack_upload_dev", "wv_device_status", "wv_matvec_dev_static",
     "wv_argmax_dev", "wv_argmax", "wv_matvec_dev_multi", "wv_matvec_dev_gather", "wv_gather_alloc", "wv_gather_open", "wv_gather_close", "wv_gather_free", "wv_gather_read", "wv_gather_signal", "wv_gather_wait", "wv_gather_sync",
-    "wv_matvec_dev_swiglu", "wv_matvec_dev_add", "wv_matvec_dev_group_gather", "wv_rmsnorm_dev", "wv_rope_cache_dev",
+    "wv_matvec_dev_swiglu", "wv_matvec_dev_add", "wv_matvec_dev_group_gather", "wv_matvec_dev_fused", "wv_rmsnorm_dev", "wv_rope_cache_dev",
     "wv_attn_decode_dev", "wv_silu_mul_dev", "wv_residual_add_dev",
     "wv_topk_sample_dev", "wv_topk_sample", "wv_decode_row", "wv_decode_row_dev",
 ]
@@ -33,6 +33,14 @@ WV_OK, WV_ESHAPE, WV_EFORMAT, WV_ENOMEM, WV_ECUDA, WV_ETIMEOUT, WV_ENOTFOUND, WV
     0, -1, -2, -3, -4, -5, -6, -7, -8)
 _NAMES = {-1: "ESHAPE", -2: "EFORMAT", -3: "ENOMEM", -4: "ECUDA", -5: "ETIMEOUT", -6: "ENOTFOUND",
           -7: "EINIT", -8: "EARG"}
+
+
+class WvFusedCall(C.Structure):
+    """WvFusedCall of include/welvet_cuda.h."""
+    _fields_ = [("keys", C.POINTER(C.c_uint64)), ("n", C.c_int), ("dx", C.c_void_p), ("y_all", C.POINTER(C.c_void_p)),
+                ("world", C.c_int), ("rank", C.c_int), ("row_offset", C.POINTER(C.c_int)), ("in_", C.c_int),
+                ("out_local", C.POINTER(C.c_int)), ("mode", C.c_int), ("dresidual", C.c_void_p), ("dnorm_gamma", C.c_void_p),
+                ("norm_eps", C.c_double)]
 
 
 class WelvetError(RuntimeError):
@@ -93,6 +101,7 @@ def lib() -> C.CDLL:
         L.wv_matvec_dev_swiglu.argtypes = [u64, u64, vp, vp, i, i, vp]
         L.wv_matvec_dev_add.argtypes = [u64, vp, vp, vp, i, i, vp]
         L.wv_matvec_dev_group_gather.argtypes = [C.POINTER(u64), i, vp, C.POINTER(vp), i, i, C.POINTER(i), i, C.POINTER(i), i, vp, vp]
+        L.wv_matvec_dev_fused.argtypes = [C.POINTER(WvFusedCall), vp]
         L.wv_rmsnorm_dev.argtypes = [vp, vp, vp, i, i, C.c_double, vp]
         L.wv_rope_cache_dev.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, C.c_double, vp]
         L.wv_attn_decode_dev.argtypes = [vp, vp, vp, vp, i, i, i, i, i, C.c_float, vp]

@@ -545,7 +545,8 @@ int wv_launch_residual_add(float* ddst, const float* dadd, int n, cudaStream_t s
 // Sharded or local group launch with fused epilogues. keys[n]; y_all[n * world] lists, matrix by matrix, every
 // rank's output vector (world == 1: just the local ones); row_offset[n] is where this rank's rows start in them.
 static int fused_launch(const char* who, const uint64_t* keys, int n, const float* dx, float* const* y_all, int world, int rank,
-                        const int* row_offset, int in, const int* out_local, int mode, const float* dres, cudaStream_t st) {
+                        const int* row_offset, int in, const int* out_local, int mode, const float* dres, cudaStream_t st,
+                        const float* dgamma = nullptr, double eps = 0.0) {
   if (!keys || !dx || !y_all || !out_local || n < 1 || n > 4) { wv_set_error("%s: bad argument (1..4 matrices)", who); return WV_EARG; }
   if (world < 1 || world > WV_MAX_PEERS || rank < 0 || rank >= world) { wv_set_error("%s: world=%d rank=%d (at most %d ranks)", who, world, rank, WV_MAX_PEERS); return WV_EARG; }
   if (mode == 1 && n != 2) { wv_set_error("%s: the gate product takes exactly two matrices", who); return WV_EARG; }
@@ -565,6 +566,8 @@ static int fused_launch(const char* who, const uint64_t* keys, int n, const floa
   fuse.mode = mode;
   fuse.residual = dres ? dres + (row_offset ? row_offset[0] : 0) : nullptr;   // indexed like the output vectors
   fuse.npeers = world > 1 ? world : 0;
+  fuse.norm_gamma = dgamma;
+  fuse.norm_eps = eps;
   float* local[4];
   for (int i = 0; i < n; i++) {
     const int off = row_offset ? row_offset[i] : 0;
@@ -572,7 +575,7 @@ static int fused_launch(const char* who, const uint64_t* keys, int n, const floa
     local[i] = own ? own + off : nullptr;
     for (int q = 0; q < world; q++) fuse.py[i][q] = y_all[i * world + q] ? y_all[i * world + q] + off : nullptr;
   }
-  const bool need_fuse = mode != 0 || dres || world > 1;
+  const bool need_fuse = mode != 0 || dres || world > 1 || dgamma;
   if (blobs[0].fast && blobs[0].format != WV_NONE) {
     wv_cur_fuse = need_fuse ? &fuse : nullptr;
     rc = wv_launch_gemv_tma_group(blobs, n, dx, local, 1, 0, n == 1 ? blobs[0].rows : 0, st);   // a single matrix carries its row range
@@ -583,6 +586,12 @@ static int fused_launch(const char* who, const uint64_t* keys, int n, const floa
     }
   }
   // Shapes or mixes the grouped kernel does not take: the same results from separate launches.
+  if (dgamma) {   // the norm as its own launch into a scratch vector
+    float* xn = reinterpret_cast<float*>(wv_scratch_take((size_t)in * 4));
+    if (!xn) { wv_set_error("%s: activation scratch too small", who); return WV_ENOMEM; }
+    if ((rc = wv_launch_rmsnorm(dx, dgamma, xn, 1, in, eps, st))) return rc;
+    dx = xn;
+  }
   if (world > 1) {
     if (mode != 0 || dres) { wv_set_error("%s: this shape has no sharded fused path", who); return WV_ESHAPE; }
     for (int i = 0; i < n; i++) {
@@ -640,6 +649,15 @@ extern "C" int wv_matvec_dev_group_gather(const uint64_t* keys, int n, const flo
   if (rc) return rc;
   return fused_launch("wv_matvec_dev_group_gather", keys, n, dx, y_all, world, rank, row_offset, in, out_local, mode, dresidual,
                       static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int wv_matvec_dev_fused(const WvFusedCall* c, void* stream) {
+  int rc = ensure_init();
+  if (rc) return rc;
+  if (!c) { wv_set_error("wv_matvec_dev_fused: null call"); return WV_EARG; }
+  if (c->dnorm_gamma && !(c->norm_eps >= 0.0)) { wv_set_error("wv_matvec_dev_fused: negative eps"); return WV_EARG; }
+  return fused_launch("wv_matvec_dev_fused", c->keys, c->n, c->dx, c->y_all, c->world, c->rank, c->row_offset, c->in, c->out_local, c->mode,
+                      c->dresidual, static_cast<cudaStream_t>(stream), c->dnorm_gamma, c->norm_eps);
 }
 
 extern "C" int wv_rmsnorm_dev(const float* dx, const float* dgamma, float* dy, int rows, int dim, double eps, void* stream) {
@@ -772,7 +790,7 @@ struct StageSlot {
   float *hx = nullptr, *hx_dev = nullptr, *dx = nullptr, *hy = nullptr, *hy_dev = nullptr;
   size_t hx_n = 0, dx_n = 0, hy_n = 0;
 };
-#define WV_STAGE_SLOTS 4
+#define WV_STAGE_SLOTS 8
 static StageSlot g_slots[WV_STAGE_SLOTS];
 static std::atomic<unsigned> g_slot_rr{0};
 

@@ -501,6 +501,8 @@ struct WvFuse {
   const float* residual;    // one matrix: y = W x + residual
   int npeers;               // > 0: rows go to py[matrix][rank] (own and peers' vectors, already offset to this rank's rows)
   float* py[4][WV_MAX_PEERS];
+  const float* norm_gamma;  // non-null: x is RMS-normalised on its way in, x_j <- x_j / sqrt(mean(x^2) + eps) * gamma_j
+  double norm_eps;
 };
 extern thread_local const WvFuse* wv_cur_fuse;
 

@@ -17,6 +17,12 @@
 #include "wv_gemv_common.cuh"
 #include "wv_dev_hooks.h"
 #include "wv_tma_common.cuh"
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <array>
+#include <map>
+#include <mutex>
+#include <tuple>
 
 #ifndef TMA_CONSUMER_WARPS
 #define TMA_CONSUMER_WARPS 16
@@ -49,6 +55,8 @@ struct TmaGeom {
   int ncp;
   unsigned pitch[5];
   unsigned part_off;
+  unsigned nsegp[5];   // column passes: a row slice of plane i is nsegp[i] innermost boxes of its tensor map
+  const void* maps;    // column passes: five tensor maps in device memory, plane i seen as {box bytes, pieces of a row, rows}
 };
 
 // The matrices one launch works through (same format, columns and group; they share x): the
@@ -71,6 +79,8 @@ struct TmaExt {
   int npeers;               // > 0: every output row goes to all ranks' vectors py[matrix][rank] instead of grp.y[matrix]
   const float* residual;    // single matrix: added to each row sum before the store (may alias the output)
   float* py[TMA_MAX_GROUP][WV_MAX_PEERS];
+  const float* norm_gamma;  // NORM instance: RMSNorm weights; x is normalised between the copy into shared memory and the records
+  double norm_eps;
 };
 struct TmaNoExt {};
 template <bool EXT> struct TmaExtArgs { using type = TmaNoExt; };
@@ -144,7 +154,7 @@ __device__ __forceinline__ void load_frag_smem(FragT<F>& f, const LaneOff& a) {
   }
 }
 
-template <int F, int RT, bool PREFETCH, bool EXT, bool MP = false>   // MP: column passes (rows wider than 16384 columns)
+template <int F, int RT, bool PREFETCH, bool EXT, bool MP = false, bool NORM = false>   // MP: column passes (rows wider than 16384 columns); NORM: RMSNorm of x in the prologue
 __global__ void __launch_bounds__(TMA_THREADS, 1)
 gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* __restrict__ xf, float* __restrict__ y,
                 int row_begin, int row_end, const TmaGeom g, int* __restrict__ err, const typename TmaExtArgs<EXT>::type ext) {
@@ -225,8 +235,8 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
       if (++ps == g.nstage) { ps = 0; wrapped = true; ppar ^= 1u; }
     };
     if constexpr (MP) {
-      // Column passes: a tile is a slice of each of its rows, one copy per row and plane, all issued by lane 0
-      // (spreading the copies over the lanes measured slower: 54 against 40 us at 8192 x 28672).
+      // Column passes: a tile is a slice of each of its rows, fetched by one tensor-map copy per plane (one bulk copy
+      // per row and plane measured 40 us at 8192 x 28672, spread over the lanes 54 us: the copy engine pays per copy).
       (void)issue_tile; (void)pcp;
       bool held = false;
       for (int cpass = 0; cpass < g.ncp && !dead; cpass++)
@@ -249,23 +259,21 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
               ok = 0;
             }
             if (ok) {
+              // one tensor-map copy per plane brings the tile's row slices in as [row][slice]; the box always has
+              // g.tr rows (rows past the matrix are zero-filled and count towards the barrier's bytes)
               unsigned bytes = 0;
 #pragma unroll
-              for (int i = 0; i < 5; i++) bytes += g.rb[i] * nr;
+              for (int i = 0; i < 5; i++) bytes += g.rb[i] * g.tr;
               mbar_expect_tx(full_bar(s), bytes);
+              const unsigned dst = smem_u32(smem) + (unsigned)s * g.stage_bytes;
+#pragma unroll
+              for (int i = 0; i < 5; i++)
+                if (g.rb[i]) tma_load_3d(dst + g.off[i], (const unsigned char*)g.maps + 128 * i, 0, cpass * (int)g.nsegp[i], row_begin + r0, full_bar(s));
             }
           }
           ok = __shfl_sync(0xffffffffu, ok, 0);
           if (!ok) { dead = true; break; }
-          const unsigned dst = smem_u32(smem) + (unsigned)s * g.stage_bytes;
-          int id = 0;
-#pragma unroll
-          for (int i = 0; i < 5; i++) {
-            if (!g.rb[i]) continue;
-            const unsigned char* pl = (const unsigned char*)ext.grp.plane[bi][i] + (size_t)(row_begin + r0) * g.pitch[i] + (size_t)cpass * g.rb[i];
-            for (int r = 0; r < nr; r++, id++)
-              if (lane == 0) bulk_g2s(dst + g.off[i] + r * g.rb[i], pl + (size_t)r * g.pitch[i], g.rb[i], full_bar(s));
-          }
+          (void)nr;
           issued++;
           if (++ps == g.nstage) { ps = 0; wrapped = true; ppar ^= 1u; }
         }
@@ -312,6 +320,15 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
 
   WV_STAMP(0);
   WV_STAMP_NS(6);
+  // RMSNorm fused into the prologue: the norm's weights do not depend on the preceding kernel, so this lane's 32 of
+  // them are requested before the wait and are there when x is
+  float4 gam[NORM ? 8 : 1];
+  if constexpr (NORM) {
+    const float4* gp = reinterpret_cast<const float4*>(ext.norm_gamma + (size_t)(live ? c : 0) * 32);
+#pragma unroll
+    for (int k = 0; k < 8; k++) gam[k] = __ldg(gp + k);
+  }
+  __shared__ double s_norm[NORM ? TMA_CONSUMER_WARPS : 1];
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   WV_STAMP(1);
@@ -340,6 +357,21 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
         if (i0 < nv) v[u] = __ldg(reinterpret_cast<const float4*>(xrow) + i);
       }
       if (lane == 0) asm volatile("red.relaxed.cta.shared::cta.add.u32 [%0], 1;" ::"r"(smem_u32(&s_xissued)) : "memory");
+      if constexpr (NORM) {
+        // Sum of squares (the reference's RMSNorm sums in float64, layers/rmsnorm/cpu.go:76-85): a thread's at most 32
+        // squares in float32 (conversions to float64 issue at a sixteenth of the float32 rate), then float64 over the
+        // warp and, by every thread after the barrier, over the 16 warp sums in a fixed order. The float32 partial sums
+        // are off by a few 1e-7 of their value; the normalised x inherits half of that.
+        float sf = 0.f;
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+          if (tid + u * TMA_CONSUMER_WARPS * 32 < nv) sf += (v[u].x * v[u].x + v[u].y * v[u].y) + (v[u].z * v[u].z + v[u].w * v[u].w);
+        }
+        double ss = (double)sf;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) s_norm[warp] = ss;
+      }
 #pragma unroll
       for (int u = 0; u < 8; u++) {
         const int i0 = tid + u * TMA_CONSUMER_WARPS * 32;
@@ -349,7 +381,17 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
       }
     } else {
       if (lane == 0) asm volatile("red.relaxed.cta.shared::cta.add.u32 [%0], 1;" ::"r"(smem_u32(&s_xissued)) : "memory");
-      for (int i = tid; i < g.cpr * 32; i += TMA_CONSUMER_WARPS * 32) xs[(i >> 5) * 33 + (i & 31)] = __ldg(xrow + i);
+      double ss = 0.0;
+      for (int i = tid; i < g.cpr * 32; i += TMA_CONSUMER_WARPS * 32) {
+        const float xv1 = __ldg(xrow + i);
+        xs[(i >> 5) * 33 + (i & 31)] = xv1;
+        if constexpr (NORM) ss += (double)xv1 * (double)xv1;
+      }
+      if constexpr (NORM) {
+#pragma unroll
+        for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) s_norm[warp] = ss;
+      }
     }
     asm volatile("bar.sync 15, %0;" ::"n"(TMA_CONSUMER_WARPS * 32) : "memory");
   };
@@ -534,6 +576,24 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   for (cp = 0; cp < npass; cp++) {
   copy_x();
   WV_STAMP(5);
+  if constexpr (NORM) {
+    double t = 0.0;
+#pragma unroll
+    for (int w = 0; w < TMA_CONSUMER_WARPS; w++) t += s_norm[w];
+    const float inv = 1.0f / sqrtf((float)(t / (double)b.cols + ext.norm_eps));
+    // every chunk is normalised in place by the one lane of row group 0 that owns it; the other row groups' warps
+    // read it after the barrier (all warps that have a row group take part; the others have left)
+    if (rg == 0 && live) {
+      float* xw = reinterpret_cast<float*>(smem + g.x_off) + (size_t)c * 33;
+#pragma unroll
+      for (int k = 0; k < 8; k++) {
+        const float gq[4] = {gam[k].x, gam[k].y, gam[k].z, gam[k].w};
+#pragma unroll
+        for (int m = 0; m < 4; m++) xw[4 * k + m] = (xw[4 * k + m] * inv) * gq[m];
+      }
+    }
+    asm volatile("bar.sync 14, %0;" ::"r"(nactive * 32) : "memory");
+  }
   if constexpr (fi.table) {
     // IQ4_NL: f32 grid values from a shared-memory table, activations stay f32
     const unsigned char* tbl = smem + g.red_off + 2u * g.nrg * g.nwc * 32 * 4;
@@ -662,6 +722,50 @@ extern "C" void wv_set_act_width(int limbs) { g_act_width = limbs; }
 int wv_act_width() { return g_act_width; }
 int wv_tc_prequant() { return g_tma_rt == 31 ? 1 : 0; }
 
+// Tensor maps for the column passes, five per matrix (one per plane), encoded once and kept in device memory: plane i is
+// seen as {box bytes, pieces of a row, rows} with a row `pitch` bytes long; a box of {box bytes, pieces per slice, tile
+// rows} is one pass's slice of a tile's rows and lands in shared memory as [row][slice]. Returns null when the driver
+// entry point or memory is missing.
+struct PassMaps { CUtensorMap m[5]; };
+static std::mutex g_pm_mu;
+static std::map<std::tuple<std::array<const void*, 5>, std::array<unsigned, 5>, unsigned, int, int>, std::pair<const void*, std::array<unsigned, 5>>> g_pass_maps;
+static const void* pass_maps(const void* const planes[5], const unsigned pitch[5], const unsigned rb[5], int rows, int tr, unsigned nsegp[5]) {
+  std::lock_guard<std::mutex> lk(g_pm_mu);
+  // every plane's address and pitch is part of the key: a later blob may reuse one plane's address but not all five
+  const auto key = std::make_tuple(std::array<const void*, 5>{planes[0], planes[1], planes[2], planes[3], planes[4]},
+                                   std::array<unsigned, 5>{pitch[0], pitch[1], pitch[2], pitch[3], pitch[4]}, rb[0], rows, tr);
+  auto it = g_pass_maps.find(key);
+  if (it != g_pass_maps.end()) { for (int i = 0; i < 5; i++) nsegp[i] = it->second.second[i]; return it->second.first; }
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) { cudaGetLastError(); return nullptr; }
+    fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  }
+  PassMaps host{};
+  std::array<unsigned, 5> nseg{};
+  for (int i = 0; i < 5; i++) {
+    if (!rb[i]) continue;
+    unsigned inner = 256;
+    while (inner >= 16 && rb[i] % inner) inner -= 16;
+    if (inner < 16 || rb[i] / inner > 256 || tr > 256) return nullptr;
+    nseg[i] = rb[i] / inner;
+    cuuint64_t dims[3] = {inner, (cuuint64_t)(pitch[i] / inner), (cuuint64_t)rows};
+    cuuint64_t strides[2] = {inner, pitch[i]};
+    cuuint32_t box[3] = {inner, nseg[i], (cuuint32_t)tr};
+    cuuint32_t estr[3] = {1, 1, 1};
+    if (fn(&host.m[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(planes[i]), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return nullptr;
+  }
+  void* dev = nullptr;
+  if (cudaMalloc(&dev, sizeof(PassMaps)) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+  if (cudaMemcpy(dev, &host, sizeof(PassMaps), cudaMemcpyHostToDevice) != cudaSuccess) { cudaGetLastError(); cudaFree(dev); return nullptr; }
+  g_pass_maps[key] = {dev, nseg};
+  for (int i = 0; i < 5; i++) nsegp[i] = nseg[i];
+  return dev;
+}
+
 template <int F, int RT, bool PF>
 static int launch_tma(const WvDevBlob* bl, int nb, const float* dx, float* const* dys, int batch, int rb_, int re, cudaStream_t st) {
   constexpr WvFmtInfo fi = wv_fmt_info(F);
@@ -720,8 +824,11 @@ static int launch_tma(const WvDevBlob* bl, int nb, const float* dx, float* const
   }
   if (g.ncp > 1) {
     // the partial sums of a CTA's band wait in shared memory between the passes
-    for (int i = 0; i < nb; i++)
-      if ((nb == 1 ? re - rb_ : bl[i].rows) / grid + 1 > TMA_GATE_ROWS) return 1;
+    if (nb != 1) return 1;
+    if ((re - rb_) / grid + 1 > TMA_GATE_ROWS) return 1;
+    const void* planes[5] = {b.lo, b.hi, b.p0, b.p1, b.km};
+    g.maps = pass_maps(planes, g.pitch, g.rb, b.rows, g.tr, g.nsegp);
+    if (!g.maps) return 1;
   }
   if (nb == 1 && !wv_cur_peers && !fuse && g.ncp == 1) {
     auto kern = gemv_tma_kernel<F, RT, PF, false>;
@@ -733,11 +840,15 @@ static int launch_tma(const WvDevBlob* bl, int nb, const float* dx, float* const
     e = launch_pdl(kern, dim3(grid, batch), dim3(TMA_THREADS), smem, st, b, xq, dx, dys[0], rb_, re, g, g_err_dev, TmaNoExt{});
   } else {
     if constexpr (RT == 4 && !PF) {   // the grouped / peer-storing variant exists for the default configuration only
-      auto kern = g.ncp > 1 ? gemv_tma_kernel<F, RT, PF, true, true> : gemv_tma_kernel<F, RT, PF, true, false>;
-      static unsigned attr_mask[2] = {0, 0};
-      if (!(attr_mask[g.ncp > 1] & (1u << dev))) {
+      const bool norm = fuse && fuse->norm_gamma;
+      if (norm && g.ncp > 1) return WV_ESHAPE;      // the fused norm needs the whole row of x at once
+      const int variant = g.ncp > 1 ? 1 : (norm ? 2 : 0);
+      auto kern = variant == 1 ? gemv_tma_kernel<F, RT, PF, true, true, false>
+                : variant == 2 ? gemv_tma_kernel<F, RT, PF, true, false, true> : gemv_tma_kernel<F, RT, PF, true, false, false>;
+      static unsigned attr_mask[3] = {0, 0, 0};
+      if (!(attr_mask[variant] & (1u << dev))) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) != cudaSuccess) { wv_set_error("gemv (tma): cannot raise the shared-memory limit"); return WV_ECUDA; }
-        attr_mask[g.ncp > 1] |= 1u << dev;
+        attr_mask[variant] |= 1u << dev;
       }
       TmaExt ext{};
       ext.grp.n = nb;
@@ -757,6 +868,8 @@ static int launch_tma(const WvDevBlob* bl, int nb, const float* dx, float* const
       if (fuse) {
         ext.mode = fuse->mode;
         ext.residual = fuse->residual;
+        ext.norm_gamma = fuse->norm_gamma;
+        ext.norm_eps = fuse->norm_eps;
         if (fuse->residual && nb != 1) return WV_ESHAPE;
         if (fuse->npeers) {
           if (batch != 1) return WV_ESHAPE;

@@ -52,6 +52,17 @@ def MatVecAddCUDA(key: int, dx: int, dresidual: int, dy: int, in_: int, out: int
     check(lib().wv_matvec_dev_add(key, dx, dresidual, dy, in_, out, stream))
 
 
+def MatVecFusedCUDA(keys, dx: int, y_all, in_: int, out_local, mode: int = 0, dresidual: Optional[int] = None,
+                    dnorm_gamma: Optional[int] = None, norm_eps: float = 0.0, world: int = 1, rank: int = 0, row_offset=None,
+                    stream: int = 0) -> None:
+    """wv_matvec_dev_fused: up to four projections on a shared x in one launch, with the RMSNorm of x in the prologue
+    and the SiLU product / residual add / stores to every rank's vectors in the epilogue, as requested.
+    keys, y_all, out_local, row_offset are ctypes arrays (uint64, void*, int, int)."""
+    from ._lib import WvFusedCall
+    call = WvFusedCall(keys, len(keys), dx, y_all, world, rank, row_offset, in_, out_local, mode, dresidual, dnorm_gamma, norm_eps)
+    check(lib().wv_matvec_dev_fused(C.byref(call), stream))
+
+
 @dataclass
 class BlockConfig:
     """Shape of one decoder block (mha.Config / swiglu.Config fields the decode path uses)."""
@@ -66,10 +77,11 @@ class BlockConfig:
 
 
 class BlockDecoder:
-    """One block's single-token decode as nine launches: RMSNorm, Q|K|V group, RoPE + cache write,
-    attention (splits, then their merge), O + residual, RMSNorm, gate|up with the SiLU product, down + residual. `keys` maps
-    q, k, v, o, gate, up, down to resident blob keys; `bufs` maps the working vectors (n1, q, k, v,
-    attn, n2, ffn) and the weights attn_norm / ffn_norm and caches cache_k / cache_v to device pointers."""
+    """One block's single-token decode as seven launches: Q|K|V group with the attention RMSNorm in its prologue, RoPE +
+    cache write, attention (splits, then their merge), O + residual, gate|up with the FFN RMSNorm in its prologue and the
+    SiLU product in its epilogue, down + residual. `keys` maps
+    q, k, v, o, gate, up, down to resident blob keys; `bufs` maps the working vectors (q, k, v,
+    attn, ffn) and the weights attn_norm / ffn_norm and caches cache_k / cache_v to device pointers."""
 
     def __init__(self, cfg: BlockConfig, keys: dict, bufs: dict):
         self.cfg, self.keys, self.bufs = cfg, keys, bufs
@@ -77,19 +89,20 @@ class BlockDecoder:
         self._qkv_keys = (C.c_uint64 * 3)(keys["q"], keys["k"], keys["v"])
         self._qkv_outs = (C.c_int * 3)(c.NumHeads * c.HeadDim, c.NumKVHeads * c.HeadDim, c.NumKVHeads * c.HeadDim)
         self._qkv_ptrs = (C.c_void_p * 3)(bufs["q"], bufs["k"], bufs["v"])
+        self._gu_keys = (C.c_uint64 * 2)(keys["gate"], keys["up"])
+        self._gu_outs = (C.c_int * 2)(c.IntermediateDim, c.IntermediateDim)
+        self._gu_ptrs = (C.c_void_p * 2)(None, bufs["ffn"])
 
     def step(self, dh: int, pos: int, stream: int = 0) -> None:
         """h (device pointer to DModel floats) is updated in place; pos is the token's position."""
         c, k, b, L = self.cfg, self.keys, self.bufs, lib()
         qd = c.NumHeads * c.HeadDim
-        RMSNormCUDA(dh, b["attn_norm"], b["n1"], 1, c.DModel, c.Eps, stream)
-        check(L.wv_matvec_dev_multi(self._qkv_keys, 3, b["n1"], self._qkv_ptrs, 1, c.DModel, self._qkv_outs, stream))
+        MatVecFusedCUDA(self._qkv_keys, dh, self._qkv_ptrs, c.DModel, self._qkv_outs, dnorm_gamma=b["attn_norm"], norm_eps=c.Eps, stream=stream)
         RoPECacheCUDA(b["q"], b["k"], b["v"], b["cache_k"], b["cache_v"], pos, c.MaxSeqLen, c.NumHeads, c.NumKVHeads, c.HeadDim, c.RoPETheta, stream)
         AttnDecodeCUDA(b["q"], b["cache_k"], b["cache_v"], b["attn"], c.NumHeads, c.NumKVHeads, c.HeadDim, min(pos + 1, c.MaxSeqLen), c.MaxSeqLen,
                        1.0 / (c.HeadDim ** 0.5), stream)
         MatVecAddCUDA(k["o"], b["attn"], dh, dh, qd, c.DModel, stream)
-        RMSNormCUDA(dh, b["ffn_norm"], b["n2"], 1, c.DModel, c.Eps, stream)
-        MatVecSwiGLUCUDA(k["gate"], k["up"], b["n2"], b["ffn"], c.DModel, c.IntermediateDim, stream)
+        MatVecFusedCUDA(self._gu_keys, dh, self._gu_ptrs, c.DModel, self._gu_outs, mode=1, dnorm_gamma=b["ffn_norm"], norm_eps=c.Eps, stream=stream)
         MatVecAddCUDA(k["down"], b["ffn"], dh, dh, c.IntermediateDim, c.DModel, stream)
 
 
@@ -125,15 +138,15 @@ class ShardedBlockDecoder:
     """BlockDecoder with every projection row-sharded over `world` ranks: each rank keeps its rows of the seven
     matrices, its GEMV kernels store their rows into every rank's vectors (peer mappings of one exchange buffer per
     rank), and arrival flags on the device order the ranks; RMSNorm, RoPE, the cache and attention are replicated.
-    Four sharded launches per block (Q|K|V, O + residual, gate|up with the SiLU product, down + residual), each
-    followed by the signal-and-wait launch when world > 1.
+    Four sharded launches per block (Q|K|V and gate|up with their RMSNorm in the prologue, the latter with the SiLU
+    product; O and down with the residual), each followed by the signal-and-wait launch when world > 1.
 
     The hidden state alternates between the vectors `ha` and `hb` of the exchange buffer: a block reads `ha`, the O
     projection writes `hb`, the down projection writes `ha` again. A rank can run at most one sharded launch ahead
     of the slowest rank (it cannot pass a wait before every rank has signalled), and no launch writes a vector that
     the previous launch's consumers read, so peers never overwrite data still in use.
 
-    keys: this rank's resident shard of q, k, v, o, gate, up, down. local: device pointers of n1, n2, attn and the
+    keys: this rank's resident shard of q, k, v, o, gate, up, down. local: device pointers of attn and the
     weights attn_norm / ffn_norm and caches cache_k / cache_v. vec / flags: dense.GatherBuffers."""
 
     def __init__(self, cfg: BlockConfig, keys: dict, local: dict, rank: int, world: int, vec, flags=None):
@@ -160,8 +173,8 @@ class ShardedBlockDecoder:
             L = lib()
             check(L.wv_gather_sync(self._flags_all, self.world, self.rank, stream))
 
-    def _gemv(self, a, n: int, dx: int, in_: int, mode: int, dres: Optional[int], stream: int, sync: bool) -> None:
-        check(lib().wv_matvec_dev_group_gather(a[0], n, dx, a[1], self.world, self.rank, a[2], in_, a[3], mode, dres, stream))
+    def _gemv(self, a, n: int, dx: int, in_: int, mode: int, dres: Optional[int], stream: int, sync: bool, gamma: Optional[int] = None) -> None:
+        MatVecFusedCUDA(a[0], dx, a[1], in_, a[3], mode, dres, gamma, self.cfg.Eps if gamma else 0.0, self.world, self.rank, a[2], stream)
         if sync:
             self._sync(stream)
 
@@ -172,15 +185,13 @@ class ShardedBlockDecoder:
         qd = c.NumHeads * c.HeadDim
         ha, hb = own + 4 * off["ha"], own + 4 * off["hb"]
         q, k, v, ffn = own + 4 * off["q"], own + 4 * off["k"], own + 4 * off["v"], own + 4 * off["ffn"]
-        RMSNormCUDA(ha, b["attn_norm"], b["n1"], 1, c.DModel, c.Eps, stream)
-        self._gemv(self._qkv, 3, b["n1"], c.DModel, 0, None, stream, sync)
+        self._gemv(self._qkv, 3, ha, c.DModel, 0, None, stream, sync, b["attn_norm"])
         RoPECacheCUDA(q, k, v, b["cache_k"], b["cache_v"], pos, c.MaxSeqLen, c.NumHeads, c.NumKVHeads, c.HeadDim, c.RoPETheta, stream)
         AttnDecodeCUDA(q, b["cache_k"], b["cache_v"], b["attn"], c.NumHeads, c.NumKVHeads, c.HeadDim, min(pos + 1, c.MaxSeqLen), c.MaxSeqLen,
                        1.0 / (c.HeadDim ** 0.5), stream)
         self._gemv(self._o, 1, b["attn"], qd, 0, ha, stream, sync)
-        RMSNormCUDA(hb, b["ffn_norm"], b["n2"], 1, c.DModel, c.Eps, stream)
-        self._gemv(self._gu, 2, b["n2"], c.DModel, 1, None, stream, sync)
+        self._gemv(self._gu, 2, hb, c.DModel, 1, None, stream, sync, b["ffn_norm"])
         self._gemv(self._down, 1, ffn, c.IntermediateDim, 0, hb, stream, sync)
 
     def launches_per_step(self) -> int:
-        return 9 + (4 if self.world > 1 else 0)
+        return 7 + (4 if self.world > 1 else 0)
