@@ -48,10 +48,10 @@ SWEEP = [("Q4_0", 2, 0, 1), ("Q4_1", 3, 0, 1), ("Q5_0", 4, 0, 1), ("Q5_1", 5, 0,
 # Measured per format but outside the timed step (named by the target, not by the sweep config).
 EXTRA = [("AffinePacked_g64", 20, 64, 1), ("BinaryPacked_g32", 19, 32, 1), ("none_f16", 0, 0, 2), ("none_bf16", 0, 0, 3), ("none_f32", 0, 0, 1)]
 NOMINAL_HBM_GBS = 8000.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from ncu captures of single launches
-# (4096x14336), next to the algorithmic bytes of the same launches: one launch streams its blob once.
-NCU_DRAM_BYTES = {"Q4_0": 36792320, "Q8_0": 66262016, "Q4_K": 38627328}
-NCU_ALGO_BYTES = {"Q4_0": 36700160, "Q8_0": 66060288, "Q4_K": 38535168}
+# DRAM bytes per launch (dram__bytes.sum.per_second x gpu__time_duration.sum) from ncu captures of single launches at
+# 4096x14336, next to the algorithmic bytes of the same launches: one launch streams its blob once.
+NCU_DRAM_BYTES = {"Q4_0": 36822016, "Q8_0": 66425856, "Q4_K": 38659840, "Q5_K": 46000640, "Q2_K": 23978240, "IQ4_NL": 36801792}
+NCU_ALGO_BYTES = {"Q4_0": 36700160, "Q8_0": 66060288, "Q4_K": 38535168, "Q5_K": 45875200, "Q2_K": 23855104, "IQ4_NL": 36700160}
 MIN_TIMED_S = 0.25   # the timed region is lengthened to at least this by replaying the step
 
 
@@ -936,7 +936,7 @@ def main():
                            "achieved": round(dom["gbs"], 1), "peak": peak, "peak_source": peak_src, "unit": "GB/s",
                            "frac": round(dom["gbs"] / peak, 3), "traffic": dom["traffic"],
                            "bytes_per_launch": int(dom["bytes"]), "us_per_launch": round(dom["us"], 2),
-                           "traffic_note": "average algorithmic bytes per launch x the ncu DRAM/algorithmic ratio of captured Q4_0, Q8_0, Q4_K launches",
+                           "traffic_note": "average algorithmic bytes per launch x the ncu DRAM/algorithmic ratio of captured Q4_0, Q8_0, Q4_K, Q5_K, Q2_K, IQ4_NL launches",
                            "slowest": brief(dom["slow"]), "fastest": brief(dom["fast"])}
         out["per_format"] = per
         if any("dequant_bitexact" in p for p in per):

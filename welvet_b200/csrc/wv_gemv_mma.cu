@@ -39,15 +39,6 @@
 #define MMA_SLOT_K 96u
 #define MMA_SLOT_META 112u
 
-#ifdef WV_PHASES  // development aid: per-CTA clock stamps
-static __device__ long long* g_dbg_mma = nullptr;
-extern "C" void wv_debug_set_buffer_mma(long long* p) { cudaMemcpyToSymbol(g_dbg_mma, &p, sizeof p); }
-#define MSTAMP(i) do { if (g_dbg_mma && threadIdx.x == 0 && (i) < 64) g_dbg_mma[blockIdx.x * 64 + (i)] = clock64(); } while (0)
-#define MSTAMP_ANY(i) do { if (g_dbg_mma && (i) < 64) g_dbg_mma[blockIdx.x * 64 + (i)] = clock64(); } while (0)
-#else
-#define MSTAMP(i) do {} while (0)
-#define MSTAMP_ANY(i) do {} while (0)
-#endif
 
 struct MmaGeom {
   int cpr;              // chunks per row
@@ -229,7 +220,6 @@ gemv_mma_kernel(const WvDevBlob b, const float* __restrict__ xf, float* __restri
 #pragma unroll
       for (int i = 0; i < 4; i++)
         if (g.np[i]) tma_load_3d(dst + g.off[i], tm[i], 0, row0, seg * (int)g.np[i], full_bar(ps));
-      MSTAMP_ANY(40 + issued);
       issued++;
       if (++ps == g.nstage) { ps = 0; wrapped = true; ppar ^= 1u; }
     };
@@ -312,9 +302,7 @@ gemv_mma_kernel(const WvDevBlob b, const float* __restrict__ xf, float* __restri
   for (int i = 0; i < PW; i++) o_p[i] = mma_swz((unsigned)((wq + 2 * i + sel) >> g.gsh) * 4u, (unsigned)gr);
 
 
-  MSTAMP(0);
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  MSTAMP(1);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   {
     // x goes into the slots; all loads are issued before the first store
@@ -344,10 +332,8 @@ gemv_mma_kernel(const WvDevBlob b, const float* __restrict__ xf, float* __restri
     }
   }
   asm volatile("bar.sync 15, %0;" ::"n"(MMA_WARPS * 32) : "memory");
-  MSTAMP(5);
   if (tid < g.cpr) mma_quantize_slot<F>(xs0 + (unsigned)tid * MMA_SLOT);
   asm volatile("bar.sync 15, %0;" ::"n"(MMA_WARPS * 32) : "memory");
-  MSTAMP(2);
   // this lane's B words and scale factor for each of its NSEG * PW chunk pairs
   // (the factors stay in shared memory when there are too many pairs for the register file)
   constexpr bool FR_REGS = NSEG * PW <= 8;
@@ -380,7 +366,6 @@ gemv_mma_kernel(const WvDevBlob b, const float* __restrict__ xf, float* __restri
         if (*(volatile int*)&s_abort) dead = true;
         else if (!mbar_wait(full_bar(fs), fpar)) { atomicCAS_system(err, 0, 600 + fs); *(volatile int*)&s_abort = 1; dead = true; }
       }
-      MSTAMP(8 + 2 * (mt * NSEG + seg));
       const unsigned st = (unsigned)fs * g.stage_bytes;   // offset of the stage from the aligned base
       const int jseg = seg * (32 * PW) + wq;   // slot index of this warp's first chunk in the segment
 #pragma unroll
@@ -428,7 +413,6 @@ gemv_mma_kernel(const WvDevBlob b, const float* __restrict__ xf, float* __restri
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar(fs));
-      MSTAMP(9 + 2 * (mt * NSEG + seg));
       if (++fs == g.nstage) { fs = 0; fpar ^= 1u; }
     }
     // 16 row sums of this block: over the quad, then over the warps
@@ -452,9 +436,7 @@ gemv_mma_kernel(const WvDevBlob b, const float* __restrict__ xf, float* __restri
       }
     }
     par ^= 1;
-    MSTAMP(36 + mt);
   }
-  MSTAMP(4);
 }
 
 // ------------------------------------------------------------------ host side

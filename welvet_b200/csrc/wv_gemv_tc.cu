@@ -39,19 +39,6 @@
 #define TC_SEG 64            // chunks per column segment
 #define TC_RB 2              // 16-row blocks per stage, at most
 
-#ifdef WV_PHASES  // development aid: per-launch, per-CTA clock stamps (entry, x may be read, x quantised, passes decided, end, tiles)
-static __device__ long long* g_dbg_tc = nullptr;
-static int g_dbg_slot = 0;
-extern "C" void wv_debug_set_buffer_tc(long long* p) { cudaMemcpyToSymbol(g_dbg_tc, &p, sizeof p); g_dbg_slot = 0; }
-#define TSTAMP_DECL long long* dbgp = (g_dbg_tc && threadIdx.x == 0) ? g_dbg_tc + ((size_t)(g.dbg_slot & 31) * 148 + blockIdx.x) * 64 : nullptr; \
-  if (dbgp) { long long t_; unsigned sm_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); asm volatile("mov.u32 %0, %%smid;" : "=r"(sm_)); dbgp[60] = t_; dbgp[62] = sm_; }
-#define TSTAMP(i) do { if (dbgp && (i) < 60) dbgp[(i)] = clock64(); } while (0)
-#define TSTAMP_END do { if (dbgp) { long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); dbgp[61] = t_; } } while (0)
-#else
-#define TSTAMP_DECL
-#define TSTAMP(i) do {} while (0)
-#define TSTAMP_END do {} while (0)
-#endif
 
 struct TcGeom {
   int cpr;               // chunks per row
@@ -62,7 +49,6 @@ struct TcGeom {
   int rb;                // 16-row blocks per stage (1 or 2)
   int gsh;               // log2(chunks per parameter group) for binary / affine
   int force_wide;        // development switch: always run the residual pass
-  int dbg_slot;          // development builds: which launch this is (slot of the stamp buffer)
   unsigned blk_bytes;    // shared-memory bytes of one 16-row block of one segment (all planes, regions 1024-aligned)
   unsigned tx_bytes;     // bytes the copy engine delivers for one block (full boxes; what lies outside the tensor is zero-filled)
   unsigned off[5];       // plane offsets inside a block (lo, hi, p0, p1, km)
@@ -489,11 +475,8 @@ gemv_tc_kernel(const WvDevBlob b, const unsigned char* __restrict__ xrec, float*
     else { p_off[u][0] = tc_param_off<F>(g, (unsigned)gq, cs0 + e_chunk); p_off[u][1] = tc_param_off<F>(g, (unsigned)gq + 8u, cs0 + e_chunk); }
   }
 
-  TSTAMP_DECL
-  TSTAMP(0);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  TSTAMP(1);
 
   // The activation record (digits in operand order, per-chunk scale factors and sums, pass count): either prepared
   // once for the whole grid by tc_xquant_kernel and brought in with one bulk copy (g.prequant), or built here by
@@ -541,12 +524,10 @@ gemv_tc_kernel(const WvDevBlob b, const unsigned char* __restrict__ xrec, float*
       bulk_g2s(sbase + g.dig_off, rec0, rec_bytes, xbar);
     }
     if (!mbar_wait(xbar, 0u)) { atomicCAS_system(err, 0, 1100); *(volatile int*)&s_abort = 1; }
-    TSTAMP(2);
     const int* rec_tail = reinterpret_cast<const int*>(smem + g.dig_off + (size_t)g.cpr * 96);
     npass = (rec_tail[0] == 2 || g.force_wide) ? 2 : 1;
   } else {
     quantise(0);
-    TSTAMP(2);
 #pragma unroll
     for (int o = 16; o; o >>= 1) { st_a += __shfl_xor_sync(0xffffffffu, st_a, o); st_s += __shfl_xor_sync(0xffffffffu, st_s, o); }
     if (lane == 0) { s_stat[warp][0] = st_a; s_stat[warp][1] = st_s; }
@@ -556,7 +537,6 @@ gemv_tc_kernel(const WvDevBlob b, const unsigned char* __restrict__ xrec, float*
     npass = (!(ta <= 0.25f * ts) || g.force_wide) ? 2 : 1;   // criterion: see tc_xquant_kernel; every thread computes the same value
   }
   if (tid == 0) *(volatile int*)&s_npass = npass;   // for the producer
-  TSTAMP(3);
 
   int fs = 0, par = 0;
   unsigned fpar = 0;
@@ -587,7 +567,6 @@ gemv_tc_kernel(const WvDevBlob b, const unsigned char* __restrict__ xrec, float*
           else if (!mbar_wait(full_bar(fs), fpar)) { atomicCAS_system(err, 0, 1000 + fs); *(volatile int*)&s_abort = 1; dead = true; }
         }
         const unsigned st = (unsigned)fs * stage_bytes;   // offset of the stage from the aligned base
-        TSTAMP(8 + 2 * (gi * g.nseg + seg));
 #pragma unroll
         for (int u = 0; u < UPW; u++) {
           const int cu = seg * TC_SEG + (warp * UPW + u) * UNIT;   // first chunk of the unit inside the row
@@ -667,7 +646,6 @@ gemv_tc_kernel(const WvDevBlob b, const unsigned char* __restrict__ xrec, float*
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_bar(fs));
-        TSTAMP(9 + 2 * (gi * g.nseg + seg));
         if (++fs == g.nstage) { fs = 0; fpar ^= 1u; }
       }
       // row sums of this group's blocks: over the quad, then over the warps
@@ -699,8 +677,6 @@ gemv_tc_kernel(const WvDevBlob b, const unsigned char* __restrict__ xrec, float*
       par ^= 1;
     }
   }
-  TSTAMP(4);
-  TSTAMP_END;
 }
 
 // ------------------------------------------------------------------ host side
@@ -809,9 +785,6 @@ static int launch_tc(const WvDevBlob& b, const float* dx, float* dy, int batch, 
   g.bar_off = tc_align(g.red_off + redb, 128u);
   const size_t smem = 1024u + g.bar_off + (2 * TC_MAX_STAGES + 1) * 8;
   g.force_wide = wv_act_width() == 3;
-#ifdef WV_PHASES
-  g.dbg_slot = g_dbg_slot++;
-#endif
   g.prequant = wv_tc_prequant();
   // scratch for the activation records (first pass and residual per batch row) and the pre-kernel's counters
   if (batch > 256) return 1;

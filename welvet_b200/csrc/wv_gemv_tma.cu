@@ -90,17 +90,6 @@ template <> struct TmaExtArgs<true> { using type = TmaExt; };
 // host can poll it without a CUDA call.
 static int* g_err_host = nullptr;
 static int* g_err_dev = nullptr;
-#ifdef WV_PHASES  // development aid: per-CTA clock stamps (start, x ready, first tile ready, end)
-static __device__ long long* g_dbg = nullptr;
-extern "C" void wv_debug_set_buffer(long long* p) { cudaMemcpyToSymbol(g_dbg, &p, sizeof p); }
-#define WV_STAMP(i) do { if (g_dbg && threadIdx.x == 0) g_dbg[blockIdx.x * 64 + (i)] = clock64(); } while (0)
-#define WV_STAMP_ANY(i) do { if (g_dbg && (i) < 64) g_dbg[blockIdx.x * 64 + (i)] = clock64(); } while (0)
-#define WV_STAMP_NS(i) do { if (g_dbg && threadIdx.x == 0) { long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_dbg[blockIdx.x * 64 + (i)] = t_; } } while (0)
-#else
-#define WV_STAMP(i) do {} while (0)
-#define WV_STAMP_ANY(i) do {} while (0)
-#define WV_STAMP_NS(i) do {} while (0)
-#endif
 
 // Per-lane shared-memory addresses (32-bit) of this lane's chunk in row 0 of its row group,
 // relative to a stage base; a row further down adds the plane's row bytes.
@@ -230,7 +219,6 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
         if (!g.rb[i]) continue;
         bulk_g2s(dst + g.off[i], (const unsigned char*)pl + (size_t)(row_begin + r0) * g.rb[i], g.rb[i] * nr, full_bar(s));
       }
-      WV_STAMP_ANY(40 + issued);
       issued++;
       if (++ps == g.nstage) { ps = 0; wrapped = true; ppar ^= 1u; }
     };
@@ -318,8 +306,6 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   const int c = wc * 32 + lane;
   const bool live = c < g.cpr;
 
-  WV_STAMP(0);
-  WV_STAMP_NS(6);
   // RMSNorm fused into the prologue: the norm's weights do not depend on the preceding kernel, so this lane's 32 of
   // them are requested before the wait and are there when x is
   float4 gam[NORM ? 8 : 1];
@@ -331,7 +317,6 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   __shared__ double s_norm[NORM ? TMA_CONSUMER_WARPS : 1];
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  WV_STAMP(1);
   // All consumer warps copy x into shared memory with coalesced loads; each chunk of 32
   // floats gets a 33-float slot so that lanes reading their own chunks element by element
   // hit 32 different banks. Every CTA starts its copy at a different place of x: all SMs
@@ -501,7 +486,6 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
       else yb = y + (size_t)blockIdx.y * b.rows + row_begin;
       FragT<F> nxt[PREFETCH ? RT : 1];
       if constexpr (PREFETCH) { if (ntiles > 0) { wait_tile(true); fetch_tile(nxt); } }
-      WV_STAMP(3);
       for (int t = 0; t < ntiles; t++) {
         FragT<F> fr[RT];
         bool fetched = true;
@@ -515,7 +499,6 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
           }
         } else {
           wait_tile(true);
-          WV_STAMP(8 + 2 * t);
           fetch_tile(fr);
         }
         float v[RT];
@@ -565,7 +548,6 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
           if (lane == (t & 31)) keep = tot;
         }
         if (((t * RT + RT - 1) & 31) == 31) flush(t * RT + RT - 32);
-        WV_STAMP(9 + 2 * t);
         if constexpr (PREFETCH) { if (!fetched) { wait_tile(true); fetch_tile(nxt); } }
       }
       if (nslots & 31) flush(nslots & ~31);
@@ -575,7 +557,6 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
   const float* xc = reinterpret_cast<const float*>(smem + g.x_off) + (size_t)(live ? c : 0) * 33;
   for (cp = 0; cp < npass; cp++) {
   copy_x();
-  WV_STAMP(5);
   if constexpr (NORM) {
     double t = 0.0;
 #pragma unroll
@@ -605,7 +586,6 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
       for (int k = 0; k < 8; k++)
         xfr[k] = make_float4(xc[WvLane<BL>::j_of(k, 0)], xc[WvLane<BL>::j_of(k, 1)], xc[WvLane<BL>::j_of(k, 2)], xc[WvLane<BL>::j_of(k, 3)]);
     }
-    WV_STAMP(2);
     const unsigned lane4 = (unsigned)lane * 4u;
     main_loop([&](const FragT<F>& f) { return chunk_value_tbl<F>(f, xfr, tbl, lane4); });
   } else {
@@ -654,7 +634,6 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
 #pragma unroll
         for (int i = 0; i < 4; i++) xr.iv[i] = 0;
       }
-      WV_STAMP(2);
       main_loop([&](const FragT<F>& f) { return idot_chunk2<F>(f, xr); });
     } else {
       XQRegs xr;
@@ -679,13 +658,10 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
 #pragma unroll
         for (int i = 0; i < 6; i++) xr.iv[i] = 0;
       }
-      WV_STAMP(2);
       main_loop([&](const FragT<F>& f) { return idot_chunk<F>(f, xr); });
     }
   }
   }
-  WV_STAMP(4);
-  WV_STAMP_NS(7);
 }
 
 // ------------------------------------------------------------------ host side
