@@ -179,6 +179,26 @@ static void gpu_checks() {
     CHECK(!l->Weights->Pack(quant::FormatQ8_0) && l->Weights->Format_ == quant::FormatQ8_0, "Store.Pack");
     CHECK(cuda::CacheBytes() <= before, "old blob evicted (%llu -> %llu)", (unsigned long long)before, (unsigned long long)cuda::CacheBytes());
   }
+  // quant.DecodeRow: a row equals the same row of Unpack; shape and FormatNone errors as in the reference
+  {
+    auto [b, ep] = quant::Pack(quant::FormatQ4_K, w, rows, cols);
+    CHECK(!ep && b, "Pack for DecodeRow");
+    if (b) {
+      auto [all, eu] = quant::Unpack(b.get());
+      std::vector<float> row(cols + 2, -1.f);
+      CHECK(!eu && !quant::DecodeRow(b.get(), 3, row), "DecodeRow");
+      bool same = !eu;
+      for (int c = 0; c < cols && same; c++) same = std::memcmp(&row[c], &all[(size_t)3 * cols + c], 4) == 0;
+      CHECK(same && row[cols] == -1.f, "DecodeRow row 3 equals Unpack row 3");
+      std::vector<float> small(cols - 1);
+      CHECK(quant::DecodeRow(b.get(), 0, small).code == WV_ESHAPE, "short dst");
+      CHECK(quant::DecodeRow(b.get(), rows, row).code == WV_ESHAPE, "row out of range");
+      CHECK(quant::DecodeRow(nullptr, 0, row).code == WV_EFORMAT, "nil blob");
+    }
+    auto [bn, en] = quant::Pack(quant::FormatNone, w, rows, cols);
+    std::vector<float> row(cols);
+    CHECK(!en && bn && quant::DecodeRow(bn.get(), 0, row).code == WV_EFORMAT, "FormatNone is refused");
+  }
   // cache budget: beyond the limit an upload is WV_ENOMEM, the reference's VRAM-full sentinel
   {
     cuda::Clear();

@@ -158,6 +158,76 @@ def test_row_shard_bookkeeping_two_ranks_gloo(tmp_path):
     assert r.returncode == 0, r.stderr[-2000:]
 
 
+BLOCK_WORKER = r'''
+import os, sys
+import numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["WV_ROOT"])
+import oracle as O
+from welvet_b200.decode import BlockConfig, projection_shapes, shard_plan, vector_layout
+dist.init_process_group("gloo")
+rank, world = dist.get_rank(), dist.get_world_size()
+cfg = BlockConfig(256, 4, 2, 64, 512, 16)
+shapes, plan, lay = projection_shapes(cfg), shard_plan(cfg, rank, world), vector_layout(cfg)
+rng = np.random.default_rng(21)
+W = {n: rng.normal(0, 0.05, s).astype(np.float32) for n, s in shapes.items()}
+ck = rng.normal(0, 1, (cfg.MaxSeqLen, 128)); cv = rng.normal(0, 1, (cfg.MaxSeqLen, 128))
+x = rng.normal(0, 1, 256).astype(np.float32); g1 = rng.normal(1, 0.1, 256).astype(np.float32); g2 = rng.normal(1, 0.1, 256).astype(np.float32)
+pos = 9
+full = {n: O.pack("Q4_K", W[n], *shapes[n]) for n in shapes}
+mine = {n: O.pack("Q4_K", W[n][plan[n][0]:plan[n][1]], plan[n][1] - plan[n][0], shapes[n][1]) for n in shapes}
+
+def walk(mv, resid):
+    """The block walk of ShardedBlockDecoder.step: mv(name, vec) is the (gathered) projection, resid adds a residual."""
+    buf = np.zeros(lay["total"], np.float32)          # this rank's exchange buffer
+    buf[lay["ha"]:lay["ha"] + 256] = x
+    n1 = O.rmsnorm(buf[lay["ha"]:lay["ha"] + 256], g1)
+    for n in ("q", "k", "v"):
+        buf[lay[n]:lay[n] + shapes[n][0]] = mv(n, n1)
+    k_, v_ = ck.copy(), cv.copy()
+    q = O.rope(buf[lay["q"]:lay["q"] + 256], pos, 4, 64)
+    k_[pos % cfg.MaxSeqLen] = O.rope(buf[lay["k"]:lay["k"] + 128], pos, 2, 64)
+    v_[pos % cfg.MaxSeqLen] = buf[lay["v"]:lay["v"] + 128]
+    attn = O.attn_decode(q, k_, v_, 4, 2, 64, pos + 1, cfg.MaxSeqLen).astype(np.float32)
+    buf[lay["hb"]:lay["hb"] + 256] = resid("o", mv("o", attn), buf[lay["ha"]:lay["ha"] + 256])
+    n2 = O.rmsnorm(buf[lay["hb"]:lay["hb"] + 256], g2)
+    buf[lay["ffn"]:lay["ffn"] + 512] = O.silu_mul(mv("gate", n2), mv("up", n2))
+    buf[lay["ha"]:lay["ha"] + 256] = resid("down", mv("down", buf[lay["ffn"]:lay["ffn"] + 512]), buf[lay["hb"]:lay["hb"] + 256])
+    return buf[lay["ha"]:lay["ha"] + 256].copy()
+
+def mv_full(n, vec): return O.matvec_simd(full[n], np.ascontiguousarray(vec, np.float32), 1)
+def mv_sharded(n, vec):
+    part = torch.from_numpy(O.matvec_simd(mine[n], np.ascontiguousarray(vec, np.float32), 1))
+    out = torch.zeros(shapes[n][0])
+    dist.all_gather_into_tensor(out, part)     # every rank's rows into every rank's vector
+    return out.numpy()
+ref = walk(mv_full, lambda n, y, r: y + r)
+got = walk(mv_sharded, lambda n, y, r: y + r)      # each owner adds its own rows of the residual: same sums
+assert np.array_equal(ref, got), "the sharded block walk differs from the unsharded one"
+# the plan tiles every projection's rows without gaps, and the vectors of the exchange buffer do not overlap
+for n, (r, _) in shapes.items():
+    assert plan[n] == (r * rank // world, r * (rank + 1) // world)
+offs = sorted((lay[k], k) for k in ("q", "k", "v", "ha", "hb", "ffn"))
+sizes = {"q": 256, "k": 128, "v": 128, "ha": 256, "hb": 256, "ffn": 512}
+for (o, k), (o2, _) in zip(offs, offs[1:] + [(lay["total"], "")]):
+    assert o + sizes[k] <= o2
+dist.barrier()
+dist.destroy_process_group()
+'''
+
+
+def test_sharded_block_walk_two_ranks_gloo(tmp_path):
+    """The row-sharded decoder block's bookkeeping (shard plan, exchange-buffer layout, hidden state alternating between two
+    vectors, residual added by the rows' owner) on two gloo ranks with the oracle standing in for the device: the sharded
+    walk equals the unsharded one bit for bit."""
+    script = tmp_path / "block_worker.py"
+    script.write_text(BLOCK_WORKER)
+    env = dict(os.environ, WV_ROOT=ROOT, MASTER_ADDR="127.0.0.1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29533", str(script)],
+                       env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+
+
 def test_activation_values_match_the_reference_enum():
     """core.ActivationType (core/layer.go:91-98): the integers are part of the call surface, so they
     are pinned here as literals; the mirror's Activate must agree with the oracle's restatement of

@@ -193,6 +193,17 @@ inline Error MatVec(const Blob* b, const std::vector<float>& x, std::vector<floa
   if (Error e = EnsureResident(b)) return e;
   return fromStatus("matvec", wv_matvec(b->Key(), x.data(), y.data(), 1, b->Cols, b->Rows));
 }
+
+// quant.DecodeRow (quant/decode_row.go:7-38): one output row of a packed Blob into dst (len >= Cols); FormatNone is
+// refused as in the reference ("use weights.DecodeRow").
+inline Error DecodeRow(const Blob* b, int row, std::vector<float>& dst) {
+  if (!b) return errorf(WV_EFORMAT, "quant: DecodeRow: nil blob");
+  if (row < 0 || row >= b->Rows || dst.size() < (size_t)b->Cols)
+    return errorf(WV_ESHAPE, "quant: DecodeRow shape row=" + std::to_string(row) + " cols=" + std::to_string(b->Cols) + " dst=" + std::to_string(dst.size()));
+  if (b->Format_ == FormatNone) return errorf(WV_EFORMAT, "quant: DecodeRow FormatNone - use weights.DecodeRow");
+  if (Error e = EnsureResident(b)) return e;
+  return fromStatus("decode_row", wv_decode_row(b->Key(), row, dst.data(), (int)dst.size()));
+}
 }  // namespace quant
 
 namespace weights {
@@ -393,6 +404,14 @@ namespace sampling {
 inline std::pair<int, Error> ArgMax(const float* d_logits, int n, void* stream = nullptr) {
   int idx = 0;
   if (int rc = wv_argmax(d_logits, n, &idx, stream)) return {0, fromStatus("argmax", rc)};
+  return {idx, Error{}};
+}
+// sampling.SampleTopK (model/sampling/topk.go:11-50) over n device floats. `u` is the uniform draw the reference takes
+// from math/rand inside the call (0 <= u <= 1); at most 1024 candidates on the device.
+inline std::pair<int, Error> SampleTopK(const float* d_logits, int n, int topK, float temperature, bool deterministic, double u,
+                                        void* stream = nullptr) {
+  int idx = 0;
+  if (int rc = wv_topk_sample(d_logits, n, topK, temperature, deterministic ? 1 : 0, u, &idx, stream)) return {0, fromStatus("topk_sample", rc)};
   return {idx, Error{}};
 }
 }  // namespace sampling
