@@ -629,7 +629,7 @@ def main():
     ap.add_argument("--impl", default="welvet_b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the per-format parity fields")
-    ap.add_argument("--e2e-callers", type=int, default=8, help="caller threads of the end-to-end measurement (the library has eight staging slots)")
+    ap.add_argument("--e2e-callers", type=int, default=4, help="caller threads of the end-to-end measurement (the library has eight staging slots)")
     ap.add_argument("--size-sweep", action="store_true", help="only: launch time against matrix size for Q4_0 / Q4_K / Q8_0 (prints its own JSON line)")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-stack decode runs (8B block stack, 70B row-sharded stack and LM head)")
     ap.add_argument("--formats", default="", help="comma list: restrict the sweep (for profiler captures)")
@@ -893,11 +893,11 @@ def main():
     E2E_CALLERS = args.e2e_callers
     if world == 1 and not args.quick:
         # Every call is the synchronous host-pointer plugin call (x copied in, y copied out inside it). The headline figure
-        # has several caller threads in flight (eight by default), as the reference's Dense is called from several goroutines
+        # has several caller threads in flight (four by default), as the reference's Dense is called from several goroutines
         # (layers/dense/cpu.go forwardTiledMC) and as the library's eight staging slots allow; one caller is reported beside it.
         from concurrent.futures import ThreadPoolExecutor
         n_e2e = max(args.steps, 20)
-        for callers in (1, E2E_CALLERS):
+        for callers in sorted({1, max(1, E2E_CALLERS)}):
             pool = ThreadPoolExecutor(callers) if callers > 1 else None
             for _ in range(3):
                 e2e_step(pool)
@@ -910,6 +910,8 @@ def main():
                 e2e_val = full_bytes / e2e_s / 1e9
             else:
                 e2e_single = full_bytes / e2e_s / 1e9
+                if E2E_CALLERS <= 1:
+                    e2e_val = e2e_single
 
     cfg = common_config(sweep)
     out = {

@@ -38,7 +38,9 @@ struct Entry {
   WvDevBlob blob;
   void* mem = nullptr;
   size_t dev_bytes = 0, wire_bytes = 0;
+  uint64_t gen = 0;       // upload generation: tells a re-uploaded key from the blob a cached launch graph was built for
 };
+static std::atomic<uint64_t> g_upload_gen{0};
 static std::mutex g_mu;                // guards the map and the byte counters
 static std::unordered_map<uint64_t, Entry> g_cache;
 static uint64_t g_cache_bytes = 0, g_cache_limit = 0;
@@ -254,6 +256,7 @@ static int upload_locked_free(uint64_t key, int format, int dtype, int rows, int
   if (cudaStreamSynchronize(g_stream) != cudaSuccess) { wv_set_error("upload sync failed"); return fail(WV_ECUDA); }
   std::lock_guard<std::mutex> lk(g_mu);
   if (g_cache.count(key)) { cudaFree(mem); return WV_OK; }
+  e.gen = ++g_upload_gen;
   g_cache[key] = e;
   g_cache_bytes += p.total;
   return WV_OK;
@@ -784,11 +787,22 @@ static int grow(float** p, size_t* cap, size_t n, bool pinned) {
 // than in transfer); the GEMV behind it is launched with programmatic stream serialisation, so its prologue overlaps
 // that kernel; y is stored by the GEMV straight into mapped pinned memory. Calls with a batch share slot 0: the
 // batched kernel's split scratch belongs to the library and takes one launch at a time.
+// A slot also keeps one instantiated CUDA graph per matrix it has served (copy-in kernel + GEMV with the slot's fixed
+// buffers): launches from several host threads are serialised by the driver, so a call that costs one graph launch instead
+// of two kernel launches leaves more of the GPU to the other callers. A graph is built on the second call for a matrix
+// (the first one may still set kernel attributes), only for the batch-1 kernels that use no scratch from the shared
+// arena, and is dropped when the key is re-uploaded or the slot's buffers move.
+struct SlotGraph { uint64_t gen = 0; cudaGraphExec_t exec = nullptr; int seen = 0; };
 struct StageSlot {
   std::mutex mu;
   cudaStream_t st = nullptr;
   float *hx = nullptr, *hx_dev = nullptr, *dx = nullptr, *hy = nullptr, *hy_dev = nullptr;
   size_t hx_n = 0, dx_n = 0, hy_n = 0;
+  std::unordered_map<uint64_t, SlotGraph> graphs;
+  void drop_graphs() {
+    for (auto& kv : graphs) if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+    graphs.clear();
+  }
 };
 #define WV_STAGE_SLOTS 8
 static StageSlot g_slots[WV_STAGE_SLOTS];
@@ -836,20 +850,46 @@ extern "C" int wv_matvec(uint64_t key, const float* x, float* y, int batch, int 
     if (slot == &g_slots[0]) slot->st = g_stream;
     else CUDA_TRY(cudaStreamCreateWithFlags(&slot->st, cudaStreamNonBlocking));
   }
+  if (slot->hx_n < nx || slot->dx_n < nx || slot->hy_n < ny) slot->drop_graphs();   // the buffers are about to move
   if ((rc = grow_mapped(&slot->hx, &slot->hx_dev, &slot->hx_n, nx)) || (rc = grow(&slot->dx, &slot->dx_n, nx, false)) ||
       (rc = grow_mapped(&slot->hy, &slot->hy_dev, &slot->hy_n, ny))) return rc;
   memcpy(slot->hx, x, nx * 4);
-  {
+  auto enqueue = [&]() -> int {
     const int n4 = (int)(nx / 4), tail = (int)(nx % 4);
     int blocks = (n4 + 255) / 256;
     if (blocks > 16) blocks = 16;
     if (blocks < 1) blocks = 1;
     stage_in_kernel<<<blocks, 256, 0, slot->st>>>(reinterpret_cast<const float4*>(slot->hx_dev), reinterpret_cast<float4*>(slot->dx), n4,
                                                  slot->hx_dev + (size_t)n4 * 4, slot->dx + (size_t)n4 * 4, tail);
-    CUDA_TRY(cudaGetLastError());
+    if (cudaGetLastError() != cudaSuccess) return WV_ECUDA;
+    return wv_launch_gemv(e.blob, slot->dx, slot->hy_dev, batch, 0, e.blob.rows, slot->st);
+  };
+  const bool graphable = batch == 1 && e.blob.fast && e.blob.format != WV_NONE && e.blob.cols <= 16384;
+  bool launched = false;
+  if (graphable) {
+    if (slot->graphs.size() >= 512 && !slot->graphs.count(key)) slot->drop_graphs();   // bound what a slot keeps
+    SlotGraph& sg = slot->graphs[key];
+    if (sg.gen != e.gen) { if (sg.exec) cudaGraphExecDestroy(sg.exec); sg = SlotGraph{}; sg.gen = e.gen; }
+    if (!sg.exec && sg.seen == 1) {
+      cudaGraph_t graph = nullptr;
+      if (cudaStreamBeginCapture(slot->st, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+        const int crc = enqueue();
+        const cudaError_t ce = cudaStreamEndCapture(slot->st, &graph);
+        if (crc == WV_OK && ce == cudaSuccess && graph && cudaGraphInstantiate(&sg.exec, graph, 0) != cudaSuccess) sg.exec = nullptr;
+        if (graph) cudaGraphDestroy(graph);
+      }
+      cudaGetLastError();
+      if (!sg.exec) sg.seen = 2;      // could not be captured: this matrix stays on plain launches
+    }
+    if (sg.exec) {
+      if (cudaGraphLaunch(sg.exec, slot->st) == cudaSuccess) launched = true;
+      else { cudaGetLastError(); cudaGraphExecDestroy(sg.exec); sg.exec = nullptr; sg.seen = 2; }
+    } else if (sg.seen == 0) sg.seen = 1;
   }
-  rc = wv_launch_gemv(e.blob, slot->dx, slot->hy_dev, batch, 0, e.blob.rows, slot->st);
-  if (rc) { wv_set_error("wv_matvec: launch failed (%d): %s", rc, cudaGetErrorString(cudaGetLastError())); return rc; }
+  if (!launched) {
+    rc = enqueue();
+    if (rc) { wv_set_error("wv_matvec: launch failed (%d): %s", rc, cudaGetErrorString(cudaGetLastError())); return rc; }
+  }
   CUDA_TRY(cudaStreamSynchronize(slot->st));
   if (int te = wv_tma_take_error()) { wv_set_error("wv_matvec: a bounded device wait ran out (code %d)", te); return WV_ETIMEOUT; }
   memcpy(y, slot->hy, ny * 4);
