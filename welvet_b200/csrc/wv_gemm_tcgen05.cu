@@ -20,10 +20,11 @@
 #include "wv_common.cuh"
 #include "wv_tma_common.cuh"
 #include <cuda.h>
+#include <cudaTypedefs.h>
 #include <mutex>
 
 #define TCG_PRODUCERS 512
-#define TCG_THREADS (TCG_PRODUCERS + 32)
+#define TCG_THREADS (TCG_PRODUCERS + 64)     // + the MMA warp and the warp whose first lane issues the X copies
 #define TCG_MAX_STAGES 6
 #define TCG_M 128
 #define TCG_KB 2            // 32-column slices per pipeline stage
@@ -160,9 +161,9 @@ struct TcgGeom {
   int y_stride;               // floats between consecutive activation rows' outputs
 };
 
-template <int F, int NB, int D>   // NB: 16-byte pieces of the X slice per producer thread; D: slices whose loads are in flight
+template <int F, int D>   // D: stages whose weight loads are in flight
 __global__ void __launch_bounds__(TCG_THREADS, 1)
-gemm_tcgen05_kernel(const WvDevBlob b, const float* __restrict__ x, float* __restrict__ y, float* __restrict__ part,
+gemm_tcgen05_kernel(const WvDevBlob b, const __grid_constant__ CUtensorMap xmap, float* __restrict__ y, float* __restrict__ part,
                     unsigned* __restrict__ counters, const TcgGeom g, int* __restrict__ err) {
   extern __shared__ __align__(1024) unsigned char tcg_smem[];
   __shared__ __align__(8) unsigned long long s_bar[2 * TCG_MAX_STAGES + 1];
@@ -183,7 +184,7 @@ gemm_tcgen05_kernel(const WvDevBlob b, const float* __restrict__ x, float* __res
 
   if (tid == 0) {
     s_abort = 0;
-    for (int s = 0; s < g.nstage; s++) { mbar_init(full_bar(s), TCG_PRODUCERS / 32); mbar_init(empty_bar(s), 1); }
+    for (int s = 0; s < g.nstage; s++) { mbar_init(full_bar(s), TCG_PRODUCERS / 32 + 1); mbar_init(empty_bar(s), 1); }
     mbar_init(done_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -195,7 +196,8 @@ gemm_tcgen05_kernel(const WvDevBlob b, const float* __restrict__ x, float* __res
   __syncthreads();
   tcg_fence_after();
   const unsigned tmem = *(volatile unsigned*)&s_tmem;
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // The weights do not depend on the preceding kernel: the producers start at once. Only the thread that copies X waits
+  // for it (X was rounded by the kernel right before this one), and nothing is stored before X has arrived.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (warp < TCG_PRODUCERS / 32) {
@@ -206,36 +208,19 @@ gemm_tcgen05_kernel(const WvDevBlob b, const float* __restrict__ x, float* __res
     const long long ch_row = (long long)row * g.cpr;
     // this thread's part of the A slice: 32 bytes of row row_l, 16-byte pieces quarter*2, quarter*2+1, swizzled by the row
     const unsigned a_off = (unsigned)(row_l >> 3) * 1024u + (unsigned)(row_l & 7) * 128u;
-    // and of the B slice: 16-byte pieces idx = tid + u * 512 -> activation row idx / 8, piece idx % 8
-    const int nb4 = g.npad * 8;
     // A stage holds TCG_KB consecutive 32-column slices (the barrier traffic and the loop's bookkeeping are paid per
     // stage, not per slice). Loads run D stages ahead of the conversion (they take about a microsecond to come back):
     // D register sets, the stage loop unrolled by D so that they are indexed statically.
     TcgRaw raw[D][TCG_KB];
-    float4 xb[D][TCG_KB][NB];
-    auto load = [&](TcgRaw (&r)[TCG_KB], float4 (&xv)[TCG_KB][NB], int it) {
+    auto load = [&](TcgRaw (&r)[TCG_KB], int it) {
 #pragma unroll
       for (int kb = 0; kb < TCG_KB; kb++) {
         const int kc = kc0 + it * TCG_KB + kb;
-        if (kc < kc1) {
-          tcg_load_raw<F>(r[kb], b, ch_row + kc, quarter);
-        } else {        // past the split's last slice: zero parameters make every weight of the slice zero
-          r[kb].lo[0] = r[kb].lo[1] = r[kb].hi[0] = r[kb].hi[1] = r[kb].km = 0u;
-          r[kb].p0 = r[kb].p1 = 0.f;
-        }
-#pragma unroll
-        for (int u = 0; u < NB; u++) {
-          const int idx = tid + u * TCG_PRODUCERS;
-          if (idx < nb4) {
-            const int br = idx >> 3;
-            xv[kb][u] = (br < g.batch && kc < kc1) ? __ldg(reinterpret_cast<const float4*>(x + (size_t)br * b.cols + (size_t)kc * 32) + (idx & 7))
-                                                     : make_float4(0.f, 0.f, 0.f, 0.f);
-          }
-        }
+        if (kc < kc1) tcg_load_raw<F>(r[kb], b, ch_row + kc, quarter);
       }
     };
 #pragma unroll
-    for (int d = 0; d < D; d++) if (d < nst) load(raw[d], xb[d], d);
+    for (int d = 0; d < D; d++) if (d < nst) load(raw[d], d);
     int s = 0;
     unsigned epar = 1;     // parity of the "empty" phase to wait for once the ring has wrapped
     bool wrapped = false;
@@ -251,6 +236,7 @@ gemm_tcgen05_kernel(const WvDevBlob b, const float* __restrict__ x, float* __res
         const unsigned st = sbase + (unsigned)s * g.stage_bytes;
 #pragma unroll
         for (int kb = 0; kb < TCG_KB; kb++) {
+          if (kc0 + it * TCG_KB + kb >= kc1) break;    // past the split's last slice: the MMA thread skips it too
           float w[8];
           tcg_convert<F>(raw[d][kb], quarter, w);
 #pragma unroll
@@ -259,21 +245,30 @@ gemm_tcgen05_kernel(const WvDevBlob b, const float* __restrict__ x, float* __res
             asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(st + kb * g.a_bytes + a_off + piece * 16u), "f"(tcg_tf32(w[4 * p])),
                          "f"(tcg_tf32(w[4 * p + 1])), "f"(tcg_tf32(w[4 * p + 2])), "f"(tcg_tf32(w[4 * p + 3])) : "memory");
           }
-#pragma unroll
-          for (int u = 0; u < NB; u++) {
-            const int idx = tid + u * TCG_PRODUCERS;
-            if (idx < nb4) {
-              const unsigned br = (unsigned)idx >> 3, piece = ((unsigned)idx & 7u) ^ (br & 7u);
-              asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};"
-                           ::"r"(st + TCG_KB * g.a_bytes + kb * g.b_bytes + (br >> 3) * 1024u + (br & 7u) * 128u + piece * 16u),
-                             "f"(tcg_tf32(xb[d][kb][u].x)), "f"(tcg_tf32(xb[d][kb][u].y)), "f"(tcg_tf32(xb[d][kb][u].z)), "f"(tcg_tf32(xb[d][kb][u].w)) : "memory");
-            }
-          }
         }
-        if (it + D < nst) load(raw[d], xb[d], it + D);
+        if (it + D < nst) load(raw[d], it + D);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(full_bar(s));      // one arrival per warp
+        if (++s == g.nstage) { s = 0; wrapped = true; epar ^= 1u; }
+      }
+    }
+  } else if (warp == TCG_PRODUCERS / 32 + 1) {
+    // ------------------------------------------------------------ X copies (one thread): a stage's slices of the rounded
+    // activations arrive by tensor-map copies with the 128-byte swizzle, i.e. already in the operand layout; rows past
+    // the batch are zero-filled by the copy engine
+    if (lane == 0) {
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      int s = 0;
+      unsigned epar = 1;
+      bool wrapped = false;
+      for (int it = 0; it < nst; it++) {
+        if (*(volatile int*)&s_abort) break;
+        if (wrapped && !mbar_wait(empty_bar(s), epar)) { atomicCAS_system(err, 0, 530 + s); *(volatile int*)&s_abort = 1; break; }
+        const int nkb = min(TCG_KB, nk - it * TCG_KB);
+        mbar_expect_tx(full_bar(s), (unsigned)nkb * g.b_bytes);
+        const unsigned st = sbase + (unsigned)s * g.stage_bytes + TCG_KB * g.a_bytes;
+        for (int kb = 0; kb < nkb; kb++) tma_load_2d(st + kb * g.b_bytes, &xmap, (kc0 + it * TCG_KB + kb) * 32, 0, full_bar(s));
         if (++s == g.nstage) { s = 0; wrapped = true; epar ^= 1u; }
       }
     }
@@ -289,6 +284,7 @@ gemm_tcgen05_kernel(const WvDevBlob b, const float* __restrict__ x, float* __res
       const unsigned st = sbase + (unsigned)s * g.stage_bytes;
 #pragma unroll
       for (int kb = 0; kb < TCG_KB; kb++) {
+        if (it * TCG_KB + kb >= nk) break;       // the split's last stage may hold one slice only
         const unsigned long long da = tcg_desc(st + kb * g.a_bytes), db = tcg_desc(st + TCG_KB * g.a_bytes + kb * g.b_bytes);
 #pragma unroll
         for (int k = 0; k < 4; k++)   // 8 TF32 values = 32 bytes further along K inside the swizzled row
@@ -359,7 +355,32 @@ gemm_tcgen05_kernel(const WvDevBlob b, const float* __restrict__ x, float* __res
   }
 }
 
+// X rounded to TF32 (round to nearest), element for element.
+__global__ void __launch_bounds__(256) tcg_round_x_kernel(const float4* __restrict__ x, float4* __restrict__ xr, size_t n4) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+    const float4 v = x[i];
+    xr[i] = make_float4(tcg_tf32(v.x), tcg_tf32(v.y), tcg_tf32(v.z), tcg_tf32(v.w));
+  }
+}
+
 // ------------------------------------------------------------------ host side
+static float* g_tcg_xr = nullptr;
+static size_t g_tcg_xr_floats = 0;
+static PFN_cuTensorMapEncodeTiled_v12000 tcg_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+    else cudaGetLastError();
+  }
+  return fn;
+}
 static float* g_tcg_part = nullptr;
 static size_t g_tcg_part_floats = 0;
 static unsigned* g_tcg_cnt = nullptr;
@@ -419,14 +440,39 @@ static int launch_tcg(const WvDevBlob& b, const float* dx, float* dy, int batch,
     }
     part = g_tcg_part; cnt = g_tcg_cnt;
   }
-  const bool small = g.npad <= 64;      // up to 64 activation rows: one piece of X per thread and slice, loads two stages (four slices) ahead
-  auto kern = small ? gemm_tcgen05_kernel<F, 1, 2> : gemm_tcgen05_kernel<F, 4, 1>;
-  static unsigned attr_mask[2] = {0, 0};
+  // X rounded to TF32 once, by a small kernel in front (each of the row tiles would otherwise round it again), into a
+  // buffer of the library; the main kernel fetches it through a tensor map encoded per call.
+  float* xr = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_tcg_mu);
+    const size_t need = (size_t)batch * b.cols;
+    if (need > g_tcg_xr_floats) {
+      cudaStreamSynchronize(st);
+      if (g_tcg_xr) cudaFree(g_tcg_xr);
+      g_tcg_xr = nullptr; g_tcg_xr_floats = 0;
+      if (cudaMalloc(&g_tcg_xr, need * 4) != cudaSuccess) { cudaGetLastError(); wv_set_error("batched matvec: %zu bytes for the rounded activations unavailable", need * 4); return WV_ENOMEM; }
+      g_tcg_xr_floats = need;
+    }
+    xr = g_tcg_xr;
+  }
+  auto enc = tcg_encode_fn();
+  if (!enc) return 1;
+  CUtensorMap xmap;
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)b.cols, (cuuint64_t)batch};
+    cuuint64_t strides[1] = {(cuuint64_t)b.cols * 4};
+    cuuint32_t box[2] = {32, (cuuint32_t)g.npad};
+    cuuint32_t estr[2] = {1, 1};
+    if (enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, xr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return 1;
+  }
+  auto kern = gemm_tcgen05_kernel<F, 4>;
+  static unsigned attr_mask = 0;
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!(attr_mask[small] & (1u << (dev & 31)))) {
+  if (!(attr_mask & (1u << (dev & 31)))) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024) != cudaSuccess) { wv_set_error("batched matvec: cannot raise the shared-memory limit"); return WV_ECUDA; }
-    attr_mask[small] |= 1u << (dev & 31);
+    attr_mask |= 1u << (dev & 31);
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(mtiles, g.ksplit); cfg.blockDim = dim3(TCG_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;
@@ -435,7 +481,18 @@ static int launch_tcg(const WvDevBlob& b, const float* dx, float* dy, int batch,
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at; cfg.numAttrs = 1;
   int* err = wv_tma_err_ptr();
-  if (cudaLaunchKernelEx(&cfg, kern, b, dx, dy, part, cnt, g, err) != cudaSuccess) { wv_set_error("batched matvec launch: %s", cudaGetErrorString(cudaGetLastError())); return WV_ECUDA; }
+  {
+    const size_t n4 = (size_t)batch * b.cols / 4;
+    cudaLaunchConfig_t rc_ = {};
+    int blocks = (int)((n4 + 255) / 256);
+    if (blocks > 2 * 148) blocks = 2 * 148;
+    rc_.gridDim = dim3(blocks); rc_.blockDim = dim3(256); rc_.stream = st;
+    rc_.attrs = at; rc_.numAttrs = 1;
+    if (cudaLaunchKernelEx(&rc_, tcg_round_x_kernel, reinterpret_cast<const float4*>(dx), reinterpret_cast<float4*>(xr), n4) != cudaSuccess) {
+      wv_set_error("batched matvec (rounding) launch: %s", cudaGetErrorString(cudaGetLastError())); return WV_ECUDA;
+    }
+  }
+  if (cudaLaunchKernelEx(&cfg, kern, b, xmap, dy, part, cnt, g, err) != cudaSuccess) { wv_set_error("batched matvec launch: %s", cudaGetErrorString(cudaGetLastError())); return WV_ECUDA; }
   return WV_OK;
 }
 

@@ -696,6 +696,16 @@ static bool batch_loop_forced() {
 #endif
 }
 
+// Smallest batch of an L2-resident matrix that goes to the tensor-core kernel (development builds: WV_BATCH_MIN overrides).
+static int batch_min() {
+#ifdef WV_DEV_HOOKS
+  static const int v = [] { const char* e = getenv("WV_BATCH_MIN"); const int n = e ? atoi(e) : 0; return n >= 2 ? n : 6; }();
+  return v;
+#else
+  return 6;
+#endif
+}
+
 int wv_launch_gemv(const WvDevBlob& b, const float* dx, float* dy, int batch, int row_begin, int row_end, cudaStream_t st) {
   if (row_end <= row_begin || batch <= 0) return WV_OK;
   const WvPeers* pp = wv_cur_peers;
@@ -705,7 +715,7 @@ int wv_launch_gemv(const WvDevBlob& b, const float* dx, float* dy, int batch, in
   // be streamed from HBM once per row, so there the tensor-core kernel takes every batch.
   const WvFmtInfo bfi = wv_fmt_info(b.format);
   const bool big = (double)b.n * (bfi.bits_lo + bfi.bits_hi) / 8.0 > 64e6;
-  if ((batch >= 6 || (batch >= 2 && big)) && !pp && !wv_cur_fuse && !g_tune_r && !wv_tma_tuning_rt() && !batch_loop_forced()) {   // a kernel forced by a tuning code keeps the batch on it
+  if ((batch >= batch_min() || (batch >= 2 && big)) && !pp && !wv_cur_fuse && !g_tune_r && !wv_tma_tuning_rt() && !batch_loop_forced()) {   // a kernel forced by a tuning code keeps the batch on it
     // Several activation rows: the tensor-core kernel streams and dequantises the matrix once for up to 256 of
     // them. What it does not take (FormatNone, ragged rows) runs row by row below.
     int rc = wv_launch_gemm_tcgen05(b, dx, dy, batch < 256 ? batch : 256, row_begin, row_end, st);
