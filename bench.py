@@ -883,30 +883,51 @@ def main():
     def e2e_call(j):
         _lib.check(L.wv_matvec(j["key"], xh[j["cols"]].ctypes.data, yh[j["key"]].ctypes.data, 1, j["cols"], j["r1"] - j["r0"]))
 
-    def e2e_step(pool):
-        if pool is None:
-            for j in jobs:
-                e2e_call(j)
-        else:
-            list(pool.map(e2e_call, jobs))
+    def e2e_run(callers, passes):
+        """Seconds per pass over the sweep with `callers` threads, each making the calls of its own share of the
+        matrices (every thread loops in its own right: a task queue between Python threads costs more per call
+        than the call)."""
+        import threading
+        shares = [jobs[i::callers] for i in range(callers)]
+        gate = threading.Barrier(callers + 1)
+        errs = []
+
+        def work(mine):
+            try:
+                for _ in range(3):                 # warm: the thread's staging slot and its launch graphs
+                    for j in mine:
+                        e2e_call(j)
+                gate.wait()
+                for _ in range(passes):
+                    for j in mine:
+                        e2e_call(j)
+            except Exception as ex:                # noqa: BLE001 - reported by the caller below
+                errs.append(ex)
+                gate.abort()
+        th = [threading.Thread(target=work, args=(m,)) for m in shares]
+        for t in th:
+            t.start()
+        try:
+            gate.wait()
+        except threading.BrokenBarrierError:
+            pass
+        t0 = time.perf_counter()
+        for t in th:
+            t.join()
+        dt = time.perf_counter() - t0
+        if errs:
+            raise errs[0]
+        return dt / passes
     e2e_val, e2e_single = None, None
     E2E_CALLERS = args.e2e_callers
     if world == 1 and not args.quick:
         # Every call is the synchronous host-pointer plugin call (x copied in, y copied out inside it). The headline figure
         # has several caller threads in flight (four by default), as the reference's Dense is called from several goroutines
         # (layers/dense/cpu.go forwardTiledMC) and as the library's eight staging slots allow; one caller is reported beside it.
-        from concurrent.futures import ThreadPoolExecutor
         n_e2e = max(args.steps, 20)
         for callers in sorted({1, max(1, E2E_CALLERS)}):
-            pool = ThreadPoolExecutor(callers) if callers > 1 else None
-            for _ in range(3):
-                e2e_step(pool)
-            t0 = time.perf_counter()
-            for _ in range(n_e2e):
-                e2e_step(pool)
-            e2e_s = (time.perf_counter() - t0) / n_e2e
-            if pool is not None:
-                pool.shutdown()
+            e2e_s = e2e_run(callers, n_e2e)
+            if callers > 1:
                 e2e_val = full_bytes / e2e_s / 1e9
             else:
                 e2e_single = full_bytes / e2e_s / 1e9

@@ -835,7 +835,10 @@ extern "C" int wv_matvec(uint64_t key, const float* x, float* y, int batch, int 
   const size_t nx = (size_t)batch * in, ny = (size_t)batch * out;
   StageSlot* slot = nullptr;
   if (batch == 1) {
-    const unsigned first = g_slot_rr.fetch_add(1);
+    // a caller thread keeps coming back to the slot it took first, so that slot's buffers and launch graphs serve it again
+    static thread_local int t_first = -1;
+    if (t_first < 0) t_first = (int)(g_slot_rr.fetch_add(1) % WV_STAGE_SLOTS);
+    const unsigned first = (unsigned)t_first;
     for (unsigned i = 0; i < WV_STAGE_SLOTS && !slot; i++) {
       StageSlot& c = g_slots[(first + i) % WV_STAGE_SLOTS];
       if (c.mu.try_lock()) slot = &c;
