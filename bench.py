@@ -50,7 +50,7 @@ EXTRA = [("AffinePacked_g64", 20, 64, 1), ("BinaryPacked_g32", 19, 32, 1), ("non
 NOMINAL_HBM_GBS = 8000.0
 # DRAM bytes per launch (dram__bytes.sum.per_second x gpu__time_duration.sum) from ncu captures of single launches at
 # 4096x14336, next to the algorithmic bytes of the same launches: one launch streams its blob once.
-NCU_DRAM_BYTES = {"Q4_0": 36822016, "Q8_0": 66425856, "Q4_K": 38659840, "Q5_K": 46000640, "Q2_K": 23978240, "IQ4_NL": 36801792}
+NCU_DRAM_BYTES = {"Q4_0": 36822016, "Q8_0": 66425856, "Q4_K": 38659840, "Q5_K": 46000640, "Q2_K": 23978240, "IQ4_NL": 36798464}
 NCU_ALGO_BYTES = {"Q4_0": 36700160, "Q8_0": 66060288, "Q4_K": 38535168, "Q5_K": 45875200, "Q2_K": 23855104, "IQ4_NL": 36700160}
 MIN_TIMED_S = 0.25   # the timed region is lengthened to at least this by replaying the step
 

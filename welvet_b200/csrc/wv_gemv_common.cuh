@@ -133,24 +133,26 @@ __device__ __forceinline__ float chunk_value(const FragT<F>& f, const float4 (&x
 }
 
 
-// IQ4_NL in the bulk-copy kernel. The grid sits in shared memory as [16 codes][64 floats] and lane l
-// uses float l of each row, so the byte offset of a code's entry is one byte permute (byte 1 = code,
-// byte 0 = 4 * lane) and lanes never collide on a bank.
+// IQ4_NL in the bulk-copy kernel. A byte of the code plane holds two weights, so the table in shared memory is
+// [256 bytes][32 lanes] of float2 {grid[low nibble], grid[high nibble]} and a byte costs one permute (byte 1 of the
+// offset = the plane byte, byte 0 = 8 * lane), one 8-byte load and one paired FMA; lane l reads slot l of a row, so
+// the 32 lanes of a load cover every bank exactly twice. xr[2w + h] = activations of bytes 2h, 2h + 1 of word w,
+// each as {low-nibble weight's, high-nibble weight's}.
 template <int F>
-__device__ __forceinline__ float chunk_value_tbl(const FragT<F>& f, const float4 (&xr)[8], const unsigned char* tbl, unsigned lane4) {
+__device__ __forceinline__ float chunk_value_tbl(const FragT<F>& f, const float4 (&xr)[8], const unsigned char* tbl, unsigned lane8) {
   static_assert(wv_fmt_info(F).table && wv_fmt_info(F).bits_lo == 4, "4-bit table format");
   float2 a0 = make_float2(0.f, 0.f), a1 = a0, b0 = a0, b1 = a0;
 #pragma unroll
-  for (int k = 0; k < 8; k++) {
-    const unsigned bytes = (f.lo[k >> 1] >> (4 * (k & 1))) & 0x0F0F0F0Fu;
-    float2 q01, q23;
-    q01.x = *reinterpret_cast<const float*>(tbl + __byte_perm(bytes, lane4, 0x5504));
-    q01.y = *reinterpret_cast<const float*>(tbl + __byte_perm(bytes, lane4, 0x5514));
-    q23.x = *reinterpret_cast<const float*>(tbl + __byte_perm(bytes, lane4, 0x5524));
-    q23.y = *reinterpret_cast<const float*>(tbl + __byte_perm(bytes, lane4, 0x5534));
-    const float2 x01 = make_float2(xr[k].x, xr[k].y), x23 = make_float2(xr[k].z, xr[k].w);
-    if (k & 1) { b0 = __ffma2_rn(q01, x01, b0); b1 = __ffma2_rn(q23, x23, b1); }
-    else { a0 = __ffma2_rn(q01, x01, a0); a1 = __ffma2_rn(q23, x23, a1); }
+  for (int w = 0; w < 4; w++) {
+    const unsigned bytes = f.lo[w];
+    const float2 q0 = *reinterpret_cast<const float2*>(tbl + __byte_perm(bytes, lane8, 0x5504));
+    const float2 q1 = *reinterpret_cast<const float2*>(tbl + __byte_perm(bytes, lane8, 0x5514));
+    const float2 q2 = *reinterpret_cast<const float2*>(tbl + __byte_perm(bytes, lane8, 0x5524));
+    const float2 q3 = *reinterpret_cast<const float2*>(tbl + __byte_perm(bytes, lane8, 0x5534));
+    a0 = __ffma2_rn(q0, make_float2(xr[2 * w].x, xr[2 * w].y), a0);
+    a1 = __ffma2_rn(q1, make_float2(xr[2 * w].z, xr[2 * w].w), a1);
+    b0 = __ffma2_rn(q2, make_float2(xr[2 * w + 1].x, xr[2 * w + 1].y), b0);
+    b1 = __ffma2_rn(q3, make_float2(xr[2 * w + 1].z, xr[2 * w + 1].w), b1);
   }
   return __uint_as_float(f.pr[0]) * (((a0.x + a0.y) + (a1.x + a1.y)) + ((b0.x + b0.y) + (b1.x + b1.y)));
 }

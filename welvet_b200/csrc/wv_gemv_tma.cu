@@ -180,8 +180,9 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if constexpr (fi.table) {
-    float* tbl = reinterpret_cast<float*>(smem + g.red_off) + 2 * g.nrg * g.nwc * 32;
-    for (int i = tid; i < 1024; i += TMA_THREADS) tbl[i] = c_grid4nl[i >> 6];   // [16 codes][64 floats]
+    // [256 code pairs][32 lanes] of float2 {grid[low nibble], grid[high nibble]}: a plane byte addresses both of its weights
+    float2* tbl = reinterpret_cast<float2*>(smem + g.red_off + 2u * g.nrg * g.nwc * 32 * 4);
+    for (int i = tid; i < 256 * 32; i += TMA_THREADS) tbl[i] = make_float2(c_grid4nl[(i >> 5) & 15], c_grid4nl[i >> 9]);
   }
   __syncthreads();
 
@@ -576,17 +577,21 @@ gemv_tma_kernel(const WvDevBlob b, const uint4* __restrict__ xqg, const float* _
     asm volatile("bar.sync 14, %0;" ::"r"(nactive * 32) : "memory");
   }
   if constexpr (fi.table) {
-    // IQ4_NL: f32 grid values from a shared-memory table, activations stay f32
+    // IQ4_NL: f32 grid values from a shared-memory table, activations stay f32. xfr[2w + h] holds, for bytes 2h and
+    // 2h + 1 of plane word w, the activations of the byte's low-nibble and high-nibble weight.
     const unsigned char* tbl = smem + g.red_off + 2u * g.nrg * g.nwc * 32 * 4;
     float4 xfr[8];
 #pragma unroll
     for (int k = 0; k < 8; k++) xfr[k] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (live) {
 #pragma unroll
-      for (int k = 0; k < 8; k++)
-        xfr[k] = make_float4(xc[WvLane<BL>::j_of(k, 0)], xc[WvLane<BL>::j_of(k, 1)], xc[WvLane<BL>::j_of(k, 2)], xc[WvLane<BL>::j_of(k, 3)]);
+      for (int w = 0; w < 4; w++)
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+          xfr[2 * w + h] = make_float4(xc[WvLane<BL>::j_of(2 * w, 2 * h)], xc[WvLane<BL>::j_of(2 * w + 1, 2 * h)],
+                                       xc[WvLane<BL>::j_of(2 * w, 2 * h + 1)], xc[WvLane<BL>::j_of(2 * w + 1, 2 * h + 1)]);
     }
-    const unsigned lane4 = (unsigned)lane * 4u;
+    const unsigned lane4 = (unsigned)lane * 8u;
     main_loop([&](const FragT<F>& f) { return chunk_value_tbl<F>(f, xfr, tbl, lane4); });
   } else {
     // Statistics of x that decide the width of the activation records, per warp, i.e. per 1024 columns (a warp's
@@ -771,7 +776,7 @@ static int launch_tma(const WvDevBlob* bl, int nb, const float* dx, float* const
   const bool gated = fuse && fuse->mode == 1;
   const unsigned gate_bytes = gated ? TMA_GATE_ROWS * 4u : 0u;
   const unsigned part_bytes = g.ncp > 1 ? (unsigned)nb * TMA_GATE_ROWS * 4u : 0u;
-  const unsigned fixed = xbytes + align128(2u * g.nrg * g.nwc * 32 * 4 + (fi.table ? 4096u : 0u)) + gate_bytes + part_bytes + 2 * TMA_MAX_STAGES * 8 + 128;
+  const unsigned fixed = xbytes + align128(2u * g.nrg * g.nwc * 32 * 4 + (fi.table ? 65536u : 0u)) + gate_bytes + part_bytes + 2 * TMA_MAX_STAGES * 8 + 128;
   const unsigned avail = 225u * 1024u;  // 227 KB per CTA minus static shared memory and slack
   if (g.stage_bytes * 2 + fixed > avail) return 1;
   int ns = (int)((avail - fixed) / g.stage_bytes);
@@ -782,7 +787,7 @@ static int launch_tma(const WvDevBlob* bl, int nb, const float* dx, float* const
   g.nstage = ns;
   g.x_off = g.stage_bytes * ns;
   g.red_off = g.x_off + xbytes;
-  g.gate_off = align128(g.red_off + 2u * g.nrg * g.nwc * 32 * 4 + (fi.table ? 4096u : 0u));
+  g.gate_off = align128(g.red_off + 2u * g.nrg * g.nwc * 32 * 4 + (fi.table ? 65536u : 0u));
   g.part_off = g.gate_off + gate_bytes;
   g.bar_off = g.part_off + part_bytes;
   const size_t smem = g.bar_off + 2 * TMA_MAX_STAGES * 8;
