@@ -215,15 +215,16 @@ dist.destroy_process_group()
 '''
 
 
-def test_sharded_block_walk_two_ranks_gloo(tmp_path):
+@pytest.mark.parametrize("world", [2, 4])
+def test_sharded_block_walk_gloo(tmp_path, world):
     """The row-sharded decoder block's bookkeeping (shard plan, exchange-buffer layout, hidden state alternating between two
-    vectors, residual added by the rows' owner) on two gloo ranks with the oracle standing in for the device: the sharded
-    walk equals the unsharded one bit for bit."""
+    vectors, residual added by the rows' owner) on two and four gloo ranks with the oracle standing in for the device: the
+    sharded walk equals the unsharded one bit for bit."""
     script = tmp_path / "block_worker.py"
     script.write_text(BLOCK_WORKER)
     env = dict(os.environ, WV_ROOT=ROOT, MASTER_ADDR="127.0.0.1")
-    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-                        "--master-addr", "127.0.0.1", "--master-port", "29533", str(script)],
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+                        "--master-addr", "127.0.0.1", "--master-port", str(29533 + world), str(script)],
                        env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stderr[-2000:]
 
